@@ -16,25 +16,28 @@ from dataclasses import dataclass
 
 import torch
 
-from ..parts.base import PagedKVNeed, StateNeed
+from ..parts.base import PagedKVNeed, StateNeed, flatten_needs
 from .manager import KVGroupSpec, StateGroupSpec
 
 
 def group_cache_layers(needs: dict[int, object], page_tokens: int):
     """Sort cache layers into key/value groups (same heads, head size, window and page dtype) and
-    state groups."""
+    state groups. A cache layer may need several things at once (a tuple: at most one set of
+    pages, any number of states): a state group lists such a layer once per state it holds there."""
     kv: dict[tuple, list[int]] = {}
     st: dict[tuple, list[int]] = {}
     for cid in sorted(needs):
-        need = needs[cid]
-        if need is None:
-            continue
-        if isinstance(need, PagedKVNeed):
-            kv.setdefault((need.num_kv_heads, need.head_dim, need.window, need.dtype), []).append(cid)
-        elif isinstance(need, StateNeed):
-            st.setdefault((tuple(need.shape), need.dtype), []).append(cid)
-        else:
-            raise TypeError(f"cache layer {cid}: unknown need {need!r}")
+        paged = 0
+        for need in flatten_needs(needs[cid]):
+            if isinstance(need, PagedKVNeed):
+                paged += 1
+                if paged > 1:
+                    raise TypeError(f"cache layer {cid}: more than one set of pages")
+                kv.setdefault((need.num_kv_heads, need.head_dim, need.window, need.dtype), []).append(cid)
+            elif isinstance(need, StateNeed):
+                st.setdefault((tuple(need.shape), need.dtype), []).append(cid)
+            else:
+                raise TypeError(f"cache layer {cid}: unknown need {need!r}")
     kv_groups = [
         KVGroupSpec(tuple(ids), nk, d, w, page_tokens, dt) for (nk, d, w, dt), ids in kv.items()
     ]
@@ -61,8 +64,17 @@ class CacheView:
     page_tokens: int
     k: torch.Tensor | None  # [pages, kv_heads, page_tokens, head_dim]
     v: torch.Tensor | None
-    state: torch.Tensor | None  # [max_requests, *shape]
+    state: torch.Tensor | None  # [max_requests, *shape]: the first (often the only) state
     writes: bool
+    states: tuple = ()  # every state of the cache layer, in the order its needs were declared
+
+    def part(self, pages: bool, first_state: int, num_states: int) -> "CacheView":
+        """The view of one of several parts that share the cache layer: with or without the
+        pages, and ``num_states`` of the states starting at ``first_state``."""
+        st = self.states[first_state : first_state + num_states]
+        return CacheView(self.group if pages else -1, self.page_tokens if pages else 0,
+                         self.k if pages else None, self.v if pages else None,
+                         st[0] if st else None, self.writes, tuple(st))
 
 
 class CachePools:
@@ -82,23 +94,50 @@ class CachePools:
             torch.zeros(len(g.cache_ids), max_requests + 1, *g.shape, dtype=g.dtype, device=device)
             for g in self.state_groups
         ]
-        self._where: dict[int, tuple[str, int, int]] = {}
+        self._pages_of: dict[int, tuple[int, int]] = {}
         for gi, g in enumerate(self.kv_groups):
             for li, cid in enumerate(g.cache_ids):
-                self._where[cid] = ("kv", gi, li)
+                self._pages_of[cid] = (gi, li)
+        self._states_of: dict[int, list[tuple[int, int]]] = {}
         for gi, g in enumerate(self.state_groups):
             for li, cid in enumerate(g.cache_ids):
-                self._where[cid] = ("state", gi, li)
+                self._states_of.setdefault(cid, []).append((gi, li))
+        self._order: dict[int, list[tuple[tuple, object]]] = {}
+        self._state_views: dict[int, tuple] = {}
+
+    def declare_order(self, needs: dict[int, object]) -> None:
+        """Remember in which order each cache layer declared its states, so that ``view().states``
+        follows it (states of equal shape keep their order within their group anyway)."""
+        self._state_views.clear()
+        for cid, need in needs.items():
+            self._order[cid] = [(tuple(n.shape), n.dtype) for n in flatten_needs(need)
+                                if isinstance(n, StateNeed)]
+
+    def _states(self, cache_id: int) -> tuple:
+        got = self._state_views.get(cache_id)
+        if got is None:
+            held = list(self._states_of.get(cache_id, ()))
+            states = []
+            for key in self._order.get(cache_id, ()):  # declared order
+                for i, (gi, li) in enumerate(held):
+                    g = self.state_groups[gi]
+                    if (tuple(g.shape), g.dtype) == key:
+                        states.append(self.state[gi][li])
+                        del held[i]
+                        break
+            states += [self.state[gi][li] for gi, li in held]
+            got = self._state_views[cache_id] = tuple(states)
+        return got
 
     def view(self, cache_id: int, writes: bool) -> CacheView:
-        where = self._where.get(cache_id)
+        where = self._pages_of.get(cache_id)
+        states = self._states(cache_id)
+        first = states[0] if states else None
         if where is None:
-            return CacheView(-1, 0, None, None, None, writes)
-        kind, gi, li = where
-        if kind == "kv":
-            t = self.kv[gi][li]
-            return CacheView(gi, self.kv_groups[gi].page_tokens, t[0], t[1], None, writes)
-        return CacheView(-1, 0, None, None, self.state[gi][li], writes)
+            return CacheView(-1, 0, None, None, first, writes, states)
+        gi, li = where
+        t = self.kv[gi][li]
+        return CacheView(gi, self.kv_groups[gi].page_tokens, t[0], t[1], first, writes, states)
 
     def spare_page(self, group: int) -> int:
         """A page of ``group`` that the manager never hands out."""

@@ -1,7 +1,7 @@
 """One registry from an architecture's name to everything needed to build its model.
 
-The name is ``config.json["architectures"][0]``; files without that key are matched on
-``model_type``. An :class:`Architecture` gives the typed config class, a function from that config
+The name is ``config.json["architectures"][0]`` (or the string under ``"architecture"``); files
+without either key are matched on ``model_type``. An :class:`Architecture` gives the typed config class, a function from that config
 to a :class:`~llmserve_b200.models.plan.ModelPlan` (the layers as data) and a function to the
 :class:`~llmserve_b200.models.plan.CheckpointLayout` (which checkpoint tensors make up which model
 parameter). Registering another architecture is one ``register_architecture`` call.
@@ -32,7 +32,9 @@ def register_architecture(arch: Architecture) -> None:
 
 
 def architecture_for(config_dict: dict[str, Any]) -> Architecture:
-    names = config_dict.get("architectures") or []
+    names = list(config_dict.get("architectures") or [])
+    if isinstance(config_dict.get("architecture"), str):  # files that name one architecture
+        names.append(config_dict["architecture"])
     for n in names:
         if n in ARCHITECTURES:
             return ARCHITECTURES[n]
@@ -68,6 +70,18 @@ def _register_builtin() -> None:
             config_cls=LlamaConfig,
             plan=llama_plan,
             checkpoint_layout=llama_checkpoint_layout,
+        )
+    )
+    from ..models.gubotar import gubotar_checkpoint_layout, gubotar_plan
+    from .gubotar import GubotarConfig
+
+    register_architecture(
+        Architecture(
+            name="Gubotar",
+            model_type="gubotar",
+            config_cls=GubotarConfig,
+            plan=gubotar_plan,
+            checkpoint_layout=gubotar_checkpoint_layout,
         )
     )
 

@@ -76,7 +76,8 @@ class ModelRunner:
         self.max_model_len = max_model_len
         if max_model_len > model.env.max_positions:
             raise ValueError("max_model_len exceeds the positions the model was built for")
-        kv_groups, state_groups = group_cache_layers(model.cache_needs(), page_tokens)
+        needs = model.cache_needs()
+        kv_groups, state_groups = group_cache_layers(needs, page_tokens)
         dtype_bytes = torch.empty(0, dtype=self.dtype).element_size()
         if num_pages is None:
             if cache_memory_bytes is None:
@@ -89,6 +90,7 @@ class ModelRunner:
             pages = list(num_pages)
         self.manager = CacheManager(kv_groups, pages, max_num_seqs)
         self.pools = CachePools(kv_groups, state_groups, pages, max_num_seqs, self.dtype, self.device)
+        self.pools.declare_order(needs)
         self.planners = model.step_planners()
         for mixer, _ in self.planners.values():
             mixer.reserve(max_num_seqs)

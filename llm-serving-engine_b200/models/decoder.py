@@ -72,9 +72,13 @@ class DecoderModel:
 
     def parts(self):
         """Every part of the model, blocks and what they are made of."""
+        def walk(part):
+            yield part
+            for child in getattr(part, "children", {}).values():
+                yield from walk(child)
+
         for block in self.blocks:
-            yield block
-            yield from block.children.values()
+            yield from walk(block)
         yield self.final_norm
         if self.embed_position is not None:
             yield self.embed_position
@@ -84,27 +88,31 @@ class DecoderModel:
         """cache id -> what the layer that fills it keeps per request (None: nothing)."""
         needs: dict[int, object] = {}
         for k, e in enumerate(self.plan.run_order):
-            mixer = self.blocks[e.layer].mixer_part()
-            need = mixer.cache_need() if mixer is not None else None
+            need = self.blocks[e.layer].cache_need()
             if e.cache not in needs:
                 needs[e.cache] = need
             elif needs[e.cache] != need:
                 raise ValueError(
                     f"run {k} (layer {e.layer}) reads cache {e.cache}, which holds {needs[e.cache]}, "
-                    f"but its mixer needs {need}"
+                    f"but it needs {need}"
                 )
         return needs
 
     def step_planners(self):
         """Distinct (plan_key, mixer, cache id) whose work lists the runner builds once a step."""
         seen = {}
+
+        def walk(mixer):
+            yield mixer
+            for b in getattr(mixer, "branches", ()):  # mixers side by side
+                yield from walk(b)
+
         for e in self.plan.run_order:
-            mixer = self.blocks[e.layer].mixer_part()
-            if mixer is None:
-                continue
-            key = mixer.plan_key()
-            if key is not None and key not in seen:
-                seen[key] = (mixer, e.cache)
+            top = self.blocks[e.layer].mixer_part()
+            for mixer in (walk(top) if top is not None else ()):
+                key = mixer.plan_key()
+                if key is not None and key not in seen:
+                    seen[key] = (mixer, e.cache)
         return seen
 
     # ------------------------------------------------------------------ forward

@@ -1,10 +1,11 @@
 """Parts a model is assembled from. Importing this package registers the built-in kinds."""
 
-from . import attention, blocks, feed_forward, norms, positions  # noqa: F401
+from . import attention, blocks, feed_forward, linear_attention, norms, parallel, positions, token_shift  # noqa: F401
 from .attention import AttentionSpec, PagedAttention
 from .base import (
     BLOCKS,
     FEED_FORWARDS,
+    INPUT_FILTERS,
     MIXERS,
     NORMS,
     POSITION_ENCODINGS,
@@ -20,7 +21,10 @@ from .base import (
     StateNeed,
     role_dtype,
 )
-from .blocks import PreNormBlock, PreNormBlockSpec
+from .blocks import BranchNormBlock, BranchNormBlockSpec, PreNormBlock, PreNormBlockSpec
+from .linear_attention import DecayLinearAttention, DecayLinearAttentionSpec
+from .parallel import ParallelMixer, ParallelMixerSpec
+from .token_shift import TokenShift, TokenShiftSpec
 from .feed_forward import SwiGLU, SwiGLUSpec
 from .norms import RMSNorm, RMSNormSpec
 from .positions import NoPositionSpec, RotaryPositionEncoding, RotarySpec
@@ -30,5 +34,7 @@ __all__ = [
     "POSITION_ENCODINGS", "Block", "BuildEnv", "FeedForward", "Mixer", "Norm", "PagedKVNeed",
     "ParamDecl", "Part", "PositionEncoding", "StateNeed", "role_dtype", "PreNormBlock",
     "PreNormBlockSpec", "SwiGLU", "SwiGLUSpec", "RMSNorm", "RMSNormSpec", "NoPositionSpec",
-    "RotaryPositionEncoding", "RotarySpec",
+    "RotaryPositionEncoding", "RotarySpec", "INPUT_FILTERS", "BranchNormBlock", "BranchNormBlockSpec",
+    "DecayLinearAttention", "DecayLinearAttentionSpec", "ParallelMixer", "ParallelMixerSpec", "TokenShift",
+    "TokenShiftSpec",
 ]

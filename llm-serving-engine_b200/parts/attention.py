@@ -12,12 +12,25 @@ Per token (src/llmserve/models/transformer.py:37-59, src/llmserve/attention.py:2
 
 ``scale`` and ``window`` are parameters of the spec. Scores, softmax and the weighted sum run in
 float32 inside the kernels.
+
+Further options of the spec, all off by default:
+
+* ``qk_norm_eps``: q and k are divided, head by head, by their root mean square and multiplied by
+  a weight of ``head_dim`` values that all heads share (one for q, one for k), before any rotation;
+* ``values_are_keys``: there is no value projection; the value of a token is its key as projected,
+  before the norm and the rotation;
+* ``head_temperature``: a learned number per query head multiplies its scores;
+* ``distance_slopes``: ``slope_h * (i - j)`` is taken off the score of query i and key j;
+* ``chunk``: query i reads key j only if ``i // chunk == j // chunk`` (positions count from the
+  start of the sequence, however the prompt was cut).
 """
 
 from __future__ import annotations
 
 from dataclasses import dataclass
 from typing import Any
+
+import torch
 
 from .base import MIXERS, POSITION_ENCODINGS, Mixer, PagedKVNeed, ParamDecl, project_into
 
@@ -32,6 +45,11 @@ class AttentionSpec:
     position: Any  # a position-encoding spec
     bias: bool = False
     window: int = 0  # 0: every earlier token; w: the last w tokens, the query's own included
+    qk_norm_eps: float | None = None
+    values_are_keys: bool = False
+    head_temperature: bool = False
+    distance_slopes: tuple[float, ...] | None = None
+    chunk: int = 0
     kind: str = "attention"
 
 
@@ -45,17 +63,31 @@ class PagedAttention(Mixer):
         self.kv_size = spec.num_kv_heads * spec.head_dim
         self.position = POSITION_ENCODINGS.build(spec.position, env)
         self.rotary = self.position.rotary_tables()
+        self.v_size = 0 if spec.values_are_keys else self.kv_size
+        # the plain path (fused projection, rotation, cache write and attention) serves none of these
+        self.extended = (spec.qk_norm_eps is not None or spec.values_are_keys or spec.head_temperature
+                         or spec.distance_slopes is not None or spec.chunk > 0)
+        self.slopes = None
+        if spec.distance_slopes is not None:
+            if len(spec.distance_slopes) != spec.num_heads:
+                raise ValueError("one distance slope per query head is needed")
+            self.slopes = torch.tensor(spec.distance_slopes, dtype=torch.float64).to(torch.float32).to(env.device)
         env.ops.check_attention_shape(spec.head_dim, env.dtype, spec.num_heads, spec.num_kv_heads)
 
     def param_decls(self):
         s = self.spec
         decls = {
-            "qkv.weight": ParamDecl((self.q_size + 2 * self.kv_size, s.hidden_size), "matrix"),
+            "qkv.weight": ParamDecl((self.q_size + self.kv_size + self.v_size, s.hidden_size), "matrix"),
             "o.weight": ParamDecl((s.hidden_size, self.q_size), "matrix"),
         }
         if s.bias:
-            decls["qkv.bias"] = ParamDecl((self.q_size + 2 * self.kv_size,), "bias")
+            decls["qkv.bias"] = ParamDecl((self.q_size + self.kv_size + self.v_size,), "bias")
             decls["o.bias"] = ParamDecl((s.hidden_size,), "bias")
+        if s.qk_norm_eps is not None:
+            decls["q_norm.weight"] = ParamDecl((s.head_dim,), "scale")
+            decls["k_norm.weight"] = ParamDecl((s.head_dim,), "scale")
+        if s.head_temperature:
+            decls["temperature"] = ParamDecl((s.num_heads,), "scale")
         return decls
 
     def bind(self, params):
@@ -63,6 +95,9 @@ class PagedAttention(Mixer):
         self.o_weight = params["o.weight"]
         self.qkv_bias = params.get("qkv.bias")
         self.o_bias = params.get("o.bias")
+        self.q_norm_weight = params.get("q_norm.weight")
+        self.k_norm_weight = params.get("k_norm.weight")
+        self.temperature = params.get("temperature")
 
     # what the cache manager has to keep for a layer of this kind
     def cache_need(self):
@@ -96,6 +131,9 @@ class PagedAttention(Mixer):
         ops = self.ops
         tables = step.block_tables[cache.group]
         cos, sin = self.rotary if self.rotary is not None else (None, None)
+        if self.extended:
+            o = self._extended(h, step, cache, tables, cos, sin)
+            return project_into(ops, o, self.o_weight, self.o_bias, self.env.residual_dtype, residual, may_defer)
         o = ops.project_attend(
             h, self.qkv_weight, self.qkv_bias,
             num_heads=s.num_heads,
@@ -117,3 +155,21 @@ class PagedAttention(Mixer):
             out_dtype=self.env.dtype,
         )
         return project_into(ops, o, self.o_weight, self.o_bias, self.env.residual_dtype, residual, may_defer)
+
+    def _extended(self, h, step, cache, tables, cos, sin):
+        """Projection (its sums unrounded), norm / rotation / cache write, attention with the
+        score options: three launches."""
+        s, ops = self.spec, self.ops
+        qkv = ops.linear(h, self.qkv_weight, self.qkv_bias, out_dtype=torch.float32)
+        q = ops.norm_rope_kv_write(
+            qkv, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,
+            values_are_keys=s.values_are_keys, q_weight=self.q_norm_weight, k_weight=self.k_norm_weight,
+            eps=s.qk_norm_eps if s.qk_norm_eps is not None else 0.0,
+            positions=step.positions, token_seq=step.token_seq, cos=cos, sin=sin,
+            k_pages=cache.k if cache.writes else None, v_pages=cache.v if cache.writes else None,
+            block_tables=tables, page_tokens=cache.page_tokens, out_dtype=self.env.dtype)
+        return ops.paged_attention(
+            q, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim, scale=s.scale,
+            window=s.window, k_pages=cache.k, v_pages=cache.v, block_tables=tables,
+            page_tokens=cache.page_tokens, step=step, plan=step.plans[self.plan_key()],
+            head_scale=self.temperature, slopes=self.slopes, chunk=s.chunk)

@@ -32,12 +32,16 @@ class ParamDecl:
     """One tensor a part owns.
 
     role: ``matrix`` (a projection weight ``[out, in]``), ``embedding`` (``[vocab, width]``),
-    ``bias`` or ``scale`` (a norm's per-channel weight). The role decides the random draw and the
-    dtype on the device.
+    ``bias``, ``scale`` (a per-channel weight around one), ``offset`` (a per-channel weight stored
+    around zero, used as one plus itself) or ``mix`` (a per-channel weight between zero and one).
+    The role decides the random draw and the dtype on the device.
     """
 
     shape: tuple[int, ...]
     role: str = "matrix"
+
+
+FLOAT32_ROLES = ("scale", "offset", "mix")  # small per-channel tensors read by 32-bit arithmetic
 
 
 def role_dtype(role: str, compute_dtype: torch.dtype, stored: torch.dtype | None = None) -> torch.dtype:
@@ -50,7 +54,7 @@ def role_dtype(role: str, compute_dtype: torch.dtype, stored: torch.dtype | None
     """
     if stored is not None and not stored.is_floating_point:
         return torch.int32
-    if role == "scale":
+    if role in FLOAT32_ROLES:
         return torch.float32
     return compute_dtype
 
@@ -96,6 +100,23 @@ class StateNeed:
     kind: str = "state"
 
 
+def flatten_needs(need) -> list:
+    """A cache need as a flat list: None is nothing, a tuple or list is each of its members."""
+    if need is None:
+        return []
+    if isinstance(need, (tuple, list)):
+        return [n for member in need for n in flatten_needs(member)]
+    return [need]
+
+
+def count_states(need) -> int:
+    return sum(isinstance(n, StateNeed) for n in flatten_needs(need))
+
+
+def has_pages(need) -> bool:
+    return any(isinstance(n, PagedKVNeed) for n in flatten_needs(need))
+
+
 # --------------------------------------------------------------------------- part base classes
 class Part:
     kind: str = ""
@@ -123,10 +144,39 @@ class Norm(Part):
     ``x`` is the float32 residual stream ``[T, H]``. If ``residual`` is given it is first added to
     ``x`` in place (in float32). Returns the normalised rows in the compute dtype. With ``rows``
     (int32 indices) only those rows are read and returned and ``x`` is left untouched.
+
+    ``add_normed(x, branch, emit) -> h | None`` is the other arrangement, for blocks that norm a
+    branch's *output*: ``x += norm(branch)`` in place; with ``emit`` the updated ``x`` is also
+    returned in the compute dtype, for the part that reads it next. ``branch`` is a float32
+    ``[T, H]`` tensor or a :class:`BranchMix`.
     """
 
     def forward(self, x, residual=None, rows=None):  # pragma: no cover - interface
         raise NotImplementedError
+
+    def add_normed(self, x, branch, emit=True):  # pragma: no cover - interface
+        raise NotImplementedError
+
+
+@dataclass
+class BranchMix:
+    """Several branch outputs that are still to be normed one by one and summed:
+
+        sum_b coefficient_b * weight_b * a_b / sqrt(mean(a_b^2) + eps)
+
+    What a mixer of parallel branches may return instead of the sum, so that a norm which is
+    applied to the sum next (``Norm.add_normed``) can do all of it while it reads the rows once.
+    ``resolve()`` computes the sum now.
+    """
+
+    ops: Any
+    branches: list  # float32 [T, H] tensors
+    weights: list  # float32 [H] tensors
+    coefficients: tuple
+    eps: float
+
+    def resolve(self):
+        return self.ops.mix_normed(self.branches, self.weights, self.coefficients, self.eps)
 
 
 class PositionEncoding(Part):
@@ -219,6 +269,12 @@ class Block(Part):
         m = self.children.get("mixer")
         return m if isinstance(m, Mixer) else None
 
+    def cache_need(self):
+        """What the block keeps per request in its cache layer: its mixer's need, unless the
+        arrangement has other parts with needs of their own (then a tuple of all of them)."""
+        m = self.mixer_part()
+        return m.cache_need() if m is not None else None
+
     def forward(self, x, pending, step, cache):  # pragma: no cover - interface
         raise NotImplementedError
 
@@ -269,6 +325,7 @@ class Registry:
 
 
 NORMS = Registry("norm")
+INPUT_FILTERS = Registry("input filter")
 POSITION_ENCODINGS = Registry("position encoding")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")

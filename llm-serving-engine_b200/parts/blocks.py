@@ -7,6 +7,14 @@
 The residual stream ``x`` is float32 and is updated in place; each add is carried out by the norm
 that reads ``x`` next, so a block returns its feed-forward output as ``pending``: a tensor, None
 (already added), or pending sums of the kernel set (see ``parts.base.settle``).
+
+``branchnorm``: the norm stands on each branch's *output* and the branches read ``x`` itself:
+
+    x <- x + norm_mixer(mixer(filter(x)));   x <- x + norm_ff(feed_forward(x))
+
+``filter`` is an optional input filter of the mixer (a token shift, say); the feed-forward is
+optional too. A filter that keeps something per request shares the block's cache layer with the
+mixer: the mixer's needs come first, the filter's states after them.
 """
 
 from __future__ import annotations
@@ -14,7 +22,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Any
 
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, settle
+from .base import BLOCKS, FEED_FORWARDS, INPUT_FILTERS, MIXERS, NORMS, Block, count_states, flatten_needs, has_pages, settle
 
 
 @dataclass(frozen=True)
@@ -51,3 +59,55 @@ class PreNormBlock(Block):
         if getattr(self.feed_forward, "accepts_residual", False):
             return x, self.feed_forward.forward(h, step, residual=x, may_defer=True)
         return x, self.feed_forward.forward(h, step)
+
+
+@dataclass(frozen=True)
+class BranchNormBlockSpec:
+    mixer: Any
+    norm_mixer: Any
+    feed_forward: Any = None  # None: the layer has no feed-forward (and no norm for it)
+    norm_ff: Any = None
+    input_filter: Any = None
+    kind: str = "branchnorm"
+
+
+@BLOCKS.register("branchnorm")
+class BranchNormBlock(Block):
+    def __init__(self, spec: BranchNormBlockSpec, env) -> None:
+        super().__init__(spec, env)
+        self.children = {"mixer": MIXERS.build(spec.mixer, env), "norm_mixer": NORMS.build(spec.norm_mixer, env)}
+        if spec.feed_forward is not None:
+            self.children["feed_forward"] = FEED_FORWARDS.build(spec.feed_forward, env)
+            self.children["norm_ff"] = NORMS.build(spec.norm_ff, env)
+        if spec.input_filter is not None:
+            self.children["filter"] = INPUT_FILTERS.build(spec.input_filter, env)
+        self.mixer = self.children["mixer"]
+        self.norm_mixer = self.children["norm_mixer"]
+        self.feed_forward = self.children.get("feed_forward")
+        self.norm_ff = self.children.get("norm_ff")
+        self.filter = self.children.get("filter")
+        need = self.mixer.cache_need()
+        self._mixer_part = (has_pages(need), 0, count_states(need))
+        self._filter_part = (False, count_states(need),
+                             count_states(self.filter.cache_need()) if self.filter is not None else 0)
+
+    def cache_need(self):
+        needs = flatten_needs(self.mixer.cache_need())
+        if self.filter is not None:
+            needs += flatten_needs(self.filter.cache_need())
+        return tuple(needs) if needs else None
+
+    def forward(self, x, pending, step, cache):
+        if pending is not None:  # a block of another arrangement came before: its add is done now
+            pending = pending.resolve() if hasattr(pending, "resolve") else pending
+            if pending is not None:
+                x += pending
+        if self.filter is not None:
+            h = self.filter.forward(x, step, cache.part(*self._filter_part))
+        else:
+            h = self.ops.cast(x, self.env.dtype)
+        a = self.mixer.forward(h, step, cache.part(*self._mixer_part))
+        h = self.norm_mixer.add_normed(x, a, emit=self.feed_forward is not None)
+        if self.feed_forward is not None:
+            self.norm_ff.add_normed(x, self.feed_forward.forward(h, step), emit=False)
+        return x, None

@@ -3,6 +3,9 @@
 ``y = x * rsqrt(mean(x^2) + eps) * w`` with the statistics, the scaling and the weight multiply in
 float32; the result is rounded once to the compute dtype. The residual add that precedes the norm
 in a pre-norm block is part of the same kernel (src/llmserve/kernels/csrc/fused_ops.cpp:52-73).
+
+``unit_offset``: the stored weight lies around zero and the norm multiplies by ``1 + w``. The sum
+is formed once, in float32, when the weight is bound; the kernels see an ordinary weight.
 """
 
 from __future__ import annotations
@@ -16,6 +19,7 @@ from .base import NORMS, Norm, ParamDecl
 class RMSNormSpec:
     size: int
     eps: float
+    unit_offset: bool = False  # multiply by 1 + w instead of w
     kind: str = "rmsnorm"
 
 
@@ -24,9 +28,18 @@ class RMSNorm(Norm):
     takes_pending_sums = True  # the kernel adds a product's pending sums as it reads the row
 
     def param_decls(self):
-        return {"weight": ParamDecl((self.spec.size,), "scale")}
+        return {"weight": ParamDecl((self.spec.size,), "offset" if self.spec.unit_offset else "scale")}
+
+    def bind(self, params):
+        w = params["weight"]
+        self.weight = (w + 1.0) if self.spec.unit_offset else w
 
     def forward(self, x, residual=None, rows=None):
         return self.ops.add_rmsnorm(
             x, residual, self.weight, self.spec.eps, out_dtype=self.env.dtype, rows=rows
         )
+
+    def add_normed(self, x, branch, emit=True):
+        """``x += norm(branch)``; returns the new ``x`` in the compute dtype if ``emit``."""
+        return self.ops.rmsnorm_add(x, branch, self.weight, self.spec.eps,
+                                    out_dtype=self.env.dtype if emit else None)

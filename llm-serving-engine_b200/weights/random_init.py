@@ -1,8 +1,8 @@
 """Random-weights mode: make a model folder (config.json, model.safetensors) from a configuration
 and a seed, or draw the same parameters straight onto a device.
 
-Draws: projection and embedding tensors N(0, 0.02^2); norm scales 1 + N(0, 0.02^2); biases
-N(0, 0.02^2). Every checkpoint tensor is drawn on the CPU in float32 from one generator, in the
+Draws: projection and embedding tensors N(0, 0.02^2); scales 1 + N(0, 0.02^2); biases and
+weights stored around zero (``offset``) N(0, 0.02^2); blending weights (``mix``) uniform in (0, 1). Every checkpoint tensor is drawn on the CPU in float32 from one generator, in the
 order of the architecture's checkpoint layout, and then rounded to the storage dtype, so a folder
 written twice from the same configuration and seed is identical, and the float32 path and any
 independent implementation that read the folder see the same values as the bfloat16 path.
@@ -23,6 +23,8 @@ STD = 0.02
 
 
 def _draw(shape, role: str, gen: torch.Generator, device="cpu") -> torch.Tensor:
+    if role == "mix":
+        return torch.rand(tuple(shape), generator=gen, dtype=torch.float32, device=device)
     t = torch.randn(tuple(shape), generator=gen, dtype=torch.float32, device=device) * STD
     return t + 1.0 if role == "scale" else t
 

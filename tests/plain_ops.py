@@ -131,7 +131,8 @@ class PlainOps:
         }
 
     def paged_attention(self, q, *, num_heads, num_kv_heads, head_dim, scale, window, k_pages,
-                        v_pages, block_tables, page_tokens, step, plan=None):
+                        v_pages, block_tables, page_tokens, step, plan=None, head_scale=None,
+                        slopes=None, chunk=0):
         T, D = q.shape[0], head_dim
         qkv = q
         q = q[:, : num_heads * D].float().reshape(T, num_heads, D)
@@ -150,10 +151,104 @@ class PlainOps:
             visible = j[None, :] <= qpos
             if window > 0:
                 visible &= (qpos - j[None, :]) < window
+            if chunk > 0:
+                visible &= (qpos // chunk) == (j[None, :] // chunk)
             sc = torch.einsum("thd,shd->hts", q[a:b], k) * scale
+            if head_scale is not None:
+                sc = sc * head_scale.float()[:, None, None]
+            if slopes is not None:
+                sc = sc - slopes.float()[:, None, None] * (qpos - j[None, :]).float()[None]
             sc = sc.masked_fill(~visible, float("-inf"))
             out[a:b] = torch.einsum("hts,shd->thd", sc.softmax(-1), v)
         return out.view(T, num_heads * D).to(qkv.dtype)
+
+    def norm_rope_kv_write(self, qkv, *, num_heads, num_kv_heads, head_dim, values_are_keys, q_weight,
+                           k_weight, eps, positions, token_seq, cos, sin, k_pages, v_pages,
+                           block_tables, page_tokens, out_dtype):
+        T, D = qkv.shape[0], head_dim
+        nv = 0 if values_are_keys else num_kv_heads
+        heads = qkv.float().view(T, num_heads + num_kv_heads + nv, D)
+        q, k = heads[:, :num_heads], heads[:, num_heads : num_heads + num_kv_heads]
+        v = k if values_are_keys else heads[:, num_heads + num_kv_heads :]
+        if q_weight is not None:
+            q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight
+            k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_weight
+        pos = positions.long()
+        if cos is not None:
+            c, s_ = cos[pos][:, None, :], sin[pos][:, None, :]
+            rot = lambda x: torch.cat([x[..., : D // 2] * c - x[..., D // 2 :] * s_,
+                                       x[..., D // 2 :] * c + x[..., : D // 2] * s_], -1)
+            q, k = rot(q), rot(k)
+        if k_pages is not None:
+            page = block_tables[token_seq.long(), pos // page_tokens].long()
+            off = pos % page_tokens
+            k_pages[page, :, off] = k.to(k_pages.dtype)
+            v_pages[page, :, off] = v.to(v_pages.dtype)
+        return q.to(out_dtype).reshape(T, num_heads * D).contiguous()
+
+    # ------------------------------------------------------------------ branch-norm blocks, state mixers
+    def cast(self, x, dtype):
+        return x if x.dtype == dtype else x.to(dtype)
+
+    def token_shift(self, x, mix, state, step, out_dtype):
+        cu, ctx, slots = step.cu_q.tolist(), step.ctx_lens.tolist(), step.state_slots.tolist()
+        out = torch.empty_like(x)
+        for s_ in range(len(ctx)):
+            a, b = cu[s_], cu[s_ + 1]
+            first = state[slots[s_]].clone() if ctx[s_] - (b - a) > 0 else torch.zeros_like(x[0])
+            prev = torch.cat([first[None], x[a : b - 1]], 0)
+            out[a:b] = x[a:b] + (prev - x[a:b]) * mix
+            state[slots[s_]] = x[b - 1]
+        return out.to(out_dtype)
+
+    def mix_normed(self, branches, weights, coefficients, eps):
+        y = 0
+        for a, w, c in zip(branches, weights, coefficients):
+            a = a.float()
+            y = y + c * (a * torch.rsqrt(a.pow(2).mean(-1, keepdim=True) + eps) * w)
+        return y
+
+    def rmsnorm_add(self, x, branch, weight, eps, out_dtype=None):
+        y = branch.resolve() if hasattr(branch, "resolve") else branch.float()
+        x += y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps) * weight
+        return None if out_dtype is None else x.to(out_dtype)
+
+    def decay_linear_attention(self, proj, *, num_heads, key_dim, value_dim, decay, state, step,
+                               activation, key_scale, cos, sin):
+        T, H, dk, dv = proj.shape[0], num_heads, key_dim, value_dim
+        p = proj.float()
+        q = p[:, : H * dk].view(T, H, dk)
+        k = p[:, H * dk : 2 * H * dk].view(T, H, dk)
+        v = p[:, 2 * H * dk : 2 * H * dk + H * dv].view(T, H, dv)
+        if activation == "silu":
+            q, k, v = (t / (1 + torch.exp(-t)) for t in (q, k, v))
+        if cos is not None:
+            half = cos.shape[1]
+            c, s_ = cos[step.positions.long()][:, None, :], sin[step.positions.long()][:, None, :]
+            rot = lambda x: torch.cat([x[..., :half] * c - x[..., half : 2 * half] * s_,
+                                       x[..., half : 2 * half] * c + x[..., :half] * s_, x[..., 2 * half :]], -1)
+            q, k = rot(q), rot(k)
+        k = k * key_scale
+        out = torch.empty(T, H, dv)
+        cu, ctx, slots = step.cu_q.tolist(), step.ctx_lens.tolist(), step.state_slots.tolist()
+        for s_ in range(len(ctx)):
+            a, b = cu[s_], cu[s_ + 1]
+            S = state[slots[s_]].clone() if ctx[s_] - (b - a) > 0 else torch.zeros_like(state[0])  # [H, dv, dk]
+            for t in range(a, b):
+                S = decay[:, None, None] * S + v[t][:, :, None] * k[t][:, None, :]
+                out[t] = torch.einsum("hvk,hk->hv", S, q[t])
+            state[slots[s_]] = S
+        return out.reshape(T, H * dv)
+
+    def gated_group_norm(self, o, proj, *, gate_offset, group, weight, eps, gate_activation, out_dtype):
+        T, N = o.shape
+        g = proj[:, gate_offset : gate_offset + N].float()
+        y = o.view(T, N // group, group)
+        y = (y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps)).reshape(T, N)
+        if weight is not None:
+            y = y * weight
+        gate = g / (1 + torch.exp(-g)) if gate_activation == "silu" else 1 / (1 + torch.exp(-g))
+        return (y * gate).to(out_dtype)
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits, temperature, top_k, top_p, min_p, seed, draw, kinds=3):
