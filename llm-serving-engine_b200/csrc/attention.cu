@@ -4,6 +4,8 @@
 // For a query at absolute position p of a sequence, with keys j of the same sequence:
 //   s_j = scale * q . k_j   for  max(0, p - window + 1) <= j <= p   (window 0: from 0)
 //   o   = sum_j softmax(s)_j * v_j
+// Optional: a factor per head on the score, a penalty slope_h * (p - j) taken off it, and chunks
+// (only keys with j / chunk == p / chunk are read); see LseAttnArgs.
 // Query head h reads key/value head h / (num_heads / num_kv_heads). Scores, the running maximum,
 // the normaliser and the weighted sum are float32 (src/llmserve/kernels/csrc/
 // paged_attention.cpp:191-243 does the same on the CPU). Keys and values are read from pages
@@ -79,6 +81,16 @@ __device__ __forceinline__ SeqInfo seq_info(const LseAttnArgs& a, int seq) {
   return s;
 }
 
+// First key that a query at position qpos may read (window and chunk together).
+__device__ __forceinline__ int first_key(const LseAttnArgs& a, int qpos) {
+  int lo = a.window > 0 ? max(0, qpos - a.window + 1) : 0;
+  if (a.chunk > 0) lo = max(lo, (qpos / a.chunk) * a.chunk);
+  return lo;
+}
+__device__ __forceinline__ float head_factor(const LseAttnArgs& a, int head) {
+  return a.head_scale ? a.scale * a.head_scale[head] : a.scale;
+}
+
 // ============================================================================ prefill, CUDA cores
 constexpr int SIMT_QT = 32;
 constexpr int SIMT_KT = (D <= 128) ? 32 : 16;
@@ -100,15 +112,18 @@ __global__ void __launch_bounds__(128) prefill_simt_kernel(const LseAttnArgs a, 
   const T* q = (const T*)a.q + (size_t)(si.q_start + (row_valid ? qi : 0)) * a.q_row_stride +
                (size_t)head * D;
   float qreg[DPT], acc[DPT];
+  const float qk_factor = head_factor(a, head);
 #pragma unroll
   for (int i = 0; i < DPT; ++i) {
-    qreg[i] = Num<T>::to_float(q[sub + 4 * i]) * a.scale;
+    qreg[i] = Num<T>::to_float(q[sub + 4 * i]) * qk_factor;
     acc[i] = 0.f;
   }
   float m = -INFINITY, l = 0.f;
   const int rows_here = min(QT, si.q_len - q0);
   const int k_end = si.pos0 + q0 + rows_here;  // one past the last key any row of the tile reads
-  const int k_first = a.window > 0 ? max(0, si.pos0 + q0 - a.window + 1) : 0;
+  const int k_first = first_key(a, si.pos0 + q0);  // of the tile's first row: no later row starts earlier
+  const int q_first = first_key(a, qpos);
+  const float slope = a.slopes ? a.slopes[head] : 0.f;
   const int* table = a.block_tables + (size_t)seq * a.table_stride;
   const T* kp = (const T*)a.k_pages;
   const T* vp = (const T*)a.v_pages;
@@ -147,9 +162,8 @@ __global__ void __launch_bounds__(128) prefill_simt_kernel(const LseAttnArgs a, 
       d += __shfl_xor_sync(0xffffffffu, d, 1);
       d += __shfl_xor_sync(0xffffffffu, d, 2);
       const int j = k0 + jj;
-      const bool ok = row_valid && j <= qpos && j >= k_first &&
-                      (a.window <= 0 || j > qpos - a.window);
-      s[jj] = ok ? d : -INFINITY;
+      const bool ok = row_valid && j <= qpos && j >= q_first;
+      s[jj] = ok ? d - slope * (float)(qpos - j) : -INFINITY;
       tile_max = fmaxf(tile_max, s[jj]);
     }
     const float m_new = fmaxf(m, tile_max);
@@ -225,7 +239,7 @@ __global__ void __launch_bounds__(MMA_THREADS, (LSE_HEAD_DIM <= 64 ? 2 : 1)) pre
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
   const int rows_here = min(QT, si.q_len - q0);
   const int k_end = si.pos0 + q0 + rows_here;
-  const int k_first = a.window > 0 ? max(0, si.pos0 + q0 - a.window + 1) : 0;
+  const int k_first = first_key(a, si.pos0 + q0);  // of the tile's first row: no later row starts earlier
   const int* table = a.block_tables + (size_t)seq * a.table_stride;
   const bf16* kp = (const bf16*)a.k_pages;
   const bf16* vp = (const bf16*)a.v_pages;
@@ -250,8 +264,14 @@ __global__ void __launch_bounds__(MMA_THREADS, (LSE_HEAD_DIM <= 64 ? 2 : 1)) pre
 #pragma unroll
   for (int i = 0; i < DB; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.f, 0.f};
-  const float sl2 = a.scale * 1.4426950408889634f;  // scores in the base-2 domain
+  // With score options the scores are finished (factor, distance penalty) when they are masked,
+  // and only the change to base 2 is left to the exponent's multiply-add.
+  const bool options = a.head_scale || a.slopes || a.chunk > 0;
+  const float qk_factor = head_factor(a, head);
+  const float slope = a.slopes ? a.slopes[head] : 0.f;
+  const float sl2 = (options ? 1.f : a.scale) * 1.4426950408889634f;  // scores in the base-2 domain
   const int qpos_r[2] = {si.pos0 + q0 + warp * 16 + g, si.pos0 + q0 + warp * 16 + g + 8};
+  const int qfirst_r[2] = {first_key(a, qpos_r[0]), first_key(a, qpos_r[1])};
   const bool valid_r[2] = {warp * 16 + g < rows_here, warp * 16 + g + 8 < rows_here};
   const int qmin_w = si.pos0 + q0 + warp * 16;  // position of this warp's first query row
 
@@ -304,7 +324,7 @@ __global__ void __launch_bounds__(MMA_THREADS, (LSE_HEAD_DIM <= 64 ? 2 : 1)) pre
     }
     // running maximum; only tiles on the diagonal, at a window's edge or at the context's start
     // need the per-element mask (rows past the portion compute garbage that is never stored)
-    const bool full_tile = k0 >= k_first && k0 + KT - 1 <= qmin_w &&
+    const bool full_tile = !options && k0 >= k_first && k0 + KT - 1 <= qmin_w &&
                            (a.window <= 0 || qmin_w + 15 - k0 < a.window);
     float tmax[2] = {-INFINITY, -INFINITY};
     if (full_tile) {
@@ -319,9 +339,9 @@ __global__ void __launch_bounds__(MMA_THREADS, (LSE_HEAD_DIM <= 64 ? 2 : 1)) pre
         for (int e = 0; e < 4; ++e) {
           const int rr = e >> 1;
           const int j = k0 + nb * 8 + t4 * 2 + (e & 1);
-          const bool ok = valid_r[rr] && j <= qpos_r[rr] && j >= k_first &&
-                          (a.window <= 0 || j > qpos_r[rr] - a.window);
-          s[nb][e] = ok ? s[nb][e] : -INFINITY;
+          const bool ok = valid_r[rr] && j <= qpos_r[rr] && j >= qfirst_r[rr];
+          const float sc = options ? s[nb][e] * qk_factor - slope * (float)(qpos_r[rr] - j) : s[nb][e];
+          s[nb][e] = ok ? sc : -INFINITY;
           tmax[rr] = fmaxf(tmax[rr], s[nb][e]);
         }
       }
@@ -480,7 +500,7 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
   const int seq = a.decode_seqs[b];
   const int tok = a.cu_q[seq];
   const int ctx = a.ctx_lens[seq];
-  const int k_first = a.window > 0 ? max(0, ctx - a.window) : 0;
+  const int k_first = first_key(a, ctx - 1);
   const int span = ctx - k_first;
   const int per = (span + a.num_splits - 1) / a.num_splits;
   const int lo = k_first + split * per;
@@ -496,11 +516,13 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
   // arithmetic above runs before the dependency wait.
   pdl_wait();  // queries and this step's key/value rows come from the kernel before this one
 
-  float qreg[GT][CPL][VEC], acc[GT][CPL][VEC], m[GT], l[GT];
+  float qreg[GT][CPL][VEC], acc[GT][CPL][VEC], m[GT], l[GT], qk_factor[GT], slope[GT];
 #pragma unroll
   for (int gq = 0; gq < GT; ++gq) {
     m[gq] = -INFINITY;
     l[gq] = 0.f;
+    qk_factor[gq] = head_factor(a, h0 + min(gq, heads_here - 1));
+    slope[gq] = a.slopes ? a.slopes[h0 + min(gq, heads_here - 1)] : 0.f;
     const T* q = (const T*)a.q + (size_t)tok * a.q_row_stride + (size_t)(h0 + min(gq, heads_here - 1)) * D;
 #pragma unroll
     for (int c = 0; c < CPL; ++c) {
@@ -509,7 +531,7 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
       if (ch < NCHUNK) qv = load16(q + ch * VEC);
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {
-        qreg[gq][c][e] = ch < NCHUNK ? Num<T>::to_float(qv.v[e]) * a.scale : 0.f;
+        qreg[gq][c][e] = ch < NCHUNK ? Num<T>::to_float(qv.v[e]) * qk_factor[gq] : 0.f;
         acc[gq][c][e] = 0.f;
       }
     }
@@ -557,6 +579,7 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
             d[u] = fmaf(qreg[gq][c][e], Num<T>::to_float(kv[u][c].v[e]), d[u]);
 #pragma unroll
         for (int o = LPK / 2; o > 0; o >>= 1) d[u] += __shfl_xor_sync(0xffffffffu, d[u], o);
+        d[u] -= slope[gq] * (float)(ctx - 1 - (j0 + u * DEC_WARPS * KPI + slot));  // the distance penalty
         if (ok[u]) m_new = fmaxf(m_new, d[u]);  // ok is uniform over the LPK lanes of a key
       }
       const float m_fin = (m_new == -INFINITY) ? 0.f : m_new;  // no key yet: everything stays 0
@@ -1585,7 +1608,7 @@ static int shift_of(int n) {
 static bool args_ok(const LseAttnArgs* a) {
   return a && (a->dtype == LSE_F32 || a->dtype == LSE_BF16) && a->num_heads > 0 &&
          a->num_kv_heads > 0 && a->num_heads % a->num_kv_heads == 0 && a->page_tokens > 0 &&
-         a->window >= 0 && (a->q || a->qkv_sums) && a->out && a->k_pages && a->v_pages && a->block_tables &&
+         a->window >= 0 && a->chunk >= 0 && (a->q || a->qkv_sums) && a->out && a->k_pages && a->v_pages && a->block_tables &&
          a->ctx_lens && a->cu_q;
 }
 
@@ -1593,13 +1616,14 @@ template <typename T>
 static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
   const int G = a->num_heads / a->num_kv_heads;
   const int ps = shift_of(a->page_tokens);
+  const bool options = a->head_scale || a->slopes || a->chunk > 0;  // served by the CUDA-core kernel only
 #if LSE_HEAD_DIM == 64 || LSE_HEAD_DIM == 128
   // On the tensor cores: one block per (partition, key/value head, sequence). Also for a single
   // head per key/value head: seven of the tile's eight columns are idle then, but the kernel
   // still issues fewer instructions per key than a dot product on the CUDA cores (head size 64,
   // batch 8, 2176 keys: 27.1 us against 30.6; batch 64: 168 against 176).
   constexpr int kMmaHeads = LSE_HEAD_DIM == 64 ? 16 : 8;  // 9..16 heads: head size 64 only
-  if (std::is_same<T, bf16>::value && G <= kMmaHeads && a->force_simt != 1) {
+  if (std::is_same<T, bf16>::value && G <= kMmaHeads && a->force_simt != 1 && !options) {
     dim3 mgrid(a->num_splits, a->num_kv_heads, a->num_decode);
     if (mgrid.y > 65535 || mgrid.z > 65535) return LSE_BAD_ARGUMENT;
     if (a->num_splits > 1 && (size_t)mgrid.y * mgrid.z > (size_t)LSE_ATTN_COUNTERS) return LSE_BAD_ARGUMENT;
@@ -1729,7 +1753,8 @@ extern "C" int lse_attn_prefill(const LseAttnArgs* a, cudaStream_t stream) {
   if (a->dtype == LSE_F32) {
     prefill_simt_kernel<float><<<grid, 128, 0, stream>>>(*a, ps);
 #if LSE_HEAD_DIM == 64
-  } else if (a->force_simt == 0 && a->num_rows > 0 && a->num_pages > 0 && atc::supported(a)) {
+  } else if (a->force_simt == 0 && a->num_rows > 0 && a->num_pages > 0 && atc::supported(a) &&
+             !(a->head_scale || a->slopes || a->chunk > 0)) {
     // 128-row tiles, like the mma.sync kernel
     return atc::launch_prefill(a, a->num_rows, a->num_pages * a->num_kv_heads * a->page_tokens,
                                a->error_flag, stream);

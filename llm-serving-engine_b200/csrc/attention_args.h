@@ -52,6 +52,13 @@ struct LseAttnArgs {
   const long long* qkv_sums;
   const float* rope_cos;
   const float* rope_sin;
+  // Options of the score, all off when null / 0. With any of them on, the CUDA-core kernels and
+  // the mma.sync kernel for portions serve the call (lse_attn_decode_takes_sums() does not hold).
+  //   s_ij = scale * head_scale[h] * q_i . k_j - slopes[h] * (i - j)
+  //   chunk > 0: query i reads key j only if i / chunk == j / chunk (absolute positions)
+  const float* head_scale;  // [num_heads] or null
+  const float* slopes;      // [num_heads] or null
+  int chunk;
 };
 
 #define LSE_ATTN_COUNTERS 65536  // words at the start of the scratch: one counter per (sequence, head group)

@@ -301,7 +301,8 @@ void paged_attention(const Tensor& q, Tensor& out, const Tensor& k_pages, const 
                      int64_t window, const Tensor& block_tables, const Tensor& ctx_lens,
                      const Tensor& cu_q, const OptTensor& tiles, int64_t num_tiles,
                      const OptTensor& decode_seqs, int64_t num_decode, int64_t num_splits,
-                     const OptTensor& scratch, int64_t force_kernel) {
+                     const OptTensor& scratch, int64_t force_kernel, const OptTensor& head_scale,
+                     const OptTensor& slopes, int64_t chunk) {
   const AttnLib& lib = attn_lib(D);
   TORCH_CHECK(q.is_cuda() && q.dim() == 2 && q.stride(1) == 1 && q.size(1) >= num_heads * D,
               "paged_attention: q must be [T, >= heads*head_dim] with unit column stride");
@@ -346,6 +347,18 @@ void paged_attention(const Tensor& q, Tensor& out, const Tensor& k_pages, const 
   a.num_rows = q.size(0);
   a.num_pages = k_pages.size(0);
   a.error_flag = error_flag();
+  if (head_scale) {
+    check_f32(*head_scale, "head_scale");
+    TORCH_CHECK(head_scale->numel() == num_heads, "paged_attention: head_scale needs one value per head");
+    a.head_scale = head_scale->data_ptr<float>();
+  }
+  if (slopes) {
+    check_f32(*slopes, "slopes");
+    TORCH_CHECK(slopes->numel() == num_heads, "paged_attention: slopes needs one value per head");
+    a.slopes = slopes->data_ptr<float>();
+  }
+  TORCH_CHECK(chunk >= 0, "paged_attention: chunk must not be negative");
+  a.chunk = (int)chunk;
   if (num_tiles > 0) {
     TORCH_CHECK(tiles.has_value(), "paged_attention: num_tiles > 0 without tiles");
     check_i32(*tiles, "tiles");
@@ -371,6 +384,190 @@ void paged_attention(const Tensor& q, Tensor& out, const Tensor& k_pages, const 
     }
     done(lib.decode(&a, stream()), "paged_attention (single tokens)");
   }
+}
+
+// ------------------------------------------------------------------ state mixers, branch norms
+int out_code(const Tensor& t, const char* what) {
+  const int c = dtype_code(t, what);
+  TORCH_CHECK(c == LSE_F32 || c == LSE_BF16, what, ": dtype must be float32 or bfloat16");
+  return c;
+}
+
+void cast_f32(const Tensor& x, Tensor& out) {
+  check_f32(x, "x");
+  check_cuda(out, "out");
+  TORCH_CHECK(out.numel() == x.numel(), "cast: sizes differ");
+  done(lse_cast(x.data_ptr<float>(), out.data_ptr(), out_code(out, "out"), x.numel(), stream()), "cast");
+}
+
+void token_shift(const Tensor& x, const Tensor& mix, Tensor& state, Tensor& out, const Tensor& token_seq,
+                 const Tensor& cu_q, const Tensor& ctx_lens, const Tensor& slots) {
+  check_f32(x, "x");
+  check_f32(mix, "mix");
+  check_f32(state, "state");
+  check_cuda(out, "out");
+  check_i32(token_seq, "token_seq");
+  check_i32(cu_q, "cu_q");
+  check_i32(ctx_lens, "ctx_lens");
+  check_i32(slots, "slots");
+  TORCH_CHECK(x.dim() == 2 && out.sizes() == x.sizes() && state.dim() == 2 && state.size(1) == x.size(1) &&
+                  mix.numel() == x.size(1),
+              "token_shift: x and out must be [T, W], state [slots, W], mix [W]");
+  TORCH_CHECK(token_seq.numel() >= x.size(0) && cu_q.numel() == ctx_lens.numel() + 1 &&
+                  slots.numel() >= ctx_lens.numel(),
+              "token_shift: the batch arrays disagree");
+  done(lse_token_shift(x.data_ptr<float>(), mix.data_ptr<float>(), state.data_ptr<float>(), out.data_ptr(),
+                       out_code(out, "out"), token_seq.data_ptr<int>(), cu_q.data_ptr<int>(),
+                       ctx_lens.data_ptr<int>(), slots.data_ptr<int>(), (int)x.size(0), (int)x.size(1),
+                       stream()),
+       "token_shift");
+}
+
+const float* opt_f32(const OptTensor& t, int64_t n, const char* what) {
+  if (!t) return nullptr;
+  check_f32(*t, what);
+  TORCH_CHECK(t->numel() == n, what, ": expected ", num(n), " values, got ", num(t->numel()));
+  return t->data_ptr<float>();
+}
+
+void rmsnorm_add(Tensor& x, const Tensor& a, const OptTensor& b, const OptTensor& wa, const OptTensor& wb,
+                 double ca, double cb, double eps_in, const Tensor& w, double eps, const OptTensor& out) {
+  check_f32(x, "x");
+  check_f32(a, "a");
+  check_f32(w, "w");
+  TORCH_CHECK(x.dim() == 2 && a.sizes() == x.sizes() && w.numel() == x.size(1), "rmsnorm_add: bad shapes");
+  const int64_t H = x.size(1);
+  const float* bp = nullptr;
+  if (b) {
+    check_f32(*b, "b");
+    TORCH_CHECK(b->sizes() == x.sizes() && wa && wb, "rmsnorm_add: a second branch needs its shape and both weights");
+    bp = b->data_ptr<float>();
+  }
+  void* op = nullptr;
+  int oc = LSE_F32;
+  if (out) {
+    check_cuda(*out, "out");
+    TORCH_CHECK(out->sizes() == x.sizes(), "rmsnorm_add: out shape differs from x");
+    op = out->data_ptr();
+    oc = out_code(*out, "out");
+  }
+  done(lse_rmsnorm_add(x.data_ptr<float>(), a.data_ptr<float>(), bp, opt_f32(wa, H, "wa"), opt_f32(wb, H, "wb"),
+                       (float)ca, (float)cb, (float)eps_in, w.data_ptr<float>(), (float)eps, op, oc,
+                       (int)x.size(0), (int)H, stream()),
+       "rmsnorm_add");
+}
+
+void mix_normed(const Tensor& a, const OptTensor& b, const Tensor& wa, const OptTensor& wb, double ca, double cb,
+                double eps, Tensor& out) {
+  check_f32(a, "a");
+  check_f32(wa, "wa");
+  check_f32(out, "out");
+  TORCH_CHECK(a.dim() == 2 && out.sizes() == a.sizes() && wa.numel() == a.size(1), "mix_normed: bad shapes");
+  const float* bp = nullptr;
+  if (b) {
+    check_f32(*b, "b");
+    TORCH_CHECK(b->sizes() == a.sizes() && wb, "mix_normed: a second branch needs its shape and weight");
+    bp = b->data_ptr<float>();
+  }
+  done(lse_mix_normed(a.data_ptr<float>(), bp, wa.data_ptr<float>(), opt_f32(wb, a.size(1), "wb"), (float)ca,
+                      (float)cb, (float)eps, out.data_ptr<float>(), (int)a.size(0), (int)a.size(1), stream()),
+       "mix_normed");
+}
+
+void gated_group_norm(const Tensor& o, const Tensor& proj, int64_t gate_offset, int64_t group,
+                      const OptTensor& weight, double eps, bool sigmoid, Tensor& out) {
+  check_f32(o, "o");
+  check_f32(proj, "proj");
+  check_cuda(out, "out");
+  TORCH_CHECK(o.dim() == 2 && proj.dim() == 2 && proj.size(0) == o.size(0) && out.sizes() == o.sizes(),
+              "gated_group_norm: o and out must be [T, N], proj [T, >= gate_offset + N]");
+  const int64_t N = o.size(1);
+  TORCH_CHECK(gate_offset >= 0 && gate_offset + N <= proj.size(1), "gated_group_norm: the gate lies outside proj");
+  TORCH_CHECK(group > 0 && N % group == 0, "gated_group_norm: group must divide the row");
+  done(lse_gated_group_norm(o.data_ptr<float>(), proj.data_ptr<float>() + gate_offset, proj.size(1), (int)o.size(0),
+                            (int)N, (int)group, opt_f32(weight, N, "weight"), (float)eps, sigmoid ? 1 : 0,
+                            out.data_ptr(), out_code(out, "out"), stream()),
+       "gated_group_norm");
+}
+
+void norm_rope_kv_write(const Tensor& qkv, Tensor& q_out, int64_t nq, int64_t nk, int64_t D, bool v_from_k,
+                        const OptTensor& qw, const OptTensor& kw, double eps, const Tensor& positions,
+                        const Tensor& token_seq, const OptTensor& cos, const OptTensor& sin,
+                        const OptTensor& k_pages, const OptTensor& v_pages, const Tensor& block_tables,
+                        int64_t page_tokens) {
+  check_f32(qkv, "qkv");
+  check_cuda(q_out, "q_out");
+  check_i32(positions, "positions");
+  check_i32(token_seq, "token_seq");
+  check_i32(block_tables, "block_tables");
+  const int64_t heads = nq + nk + (v_from_k ? 0 : nk);
+  TORCH_CHECK(qkv.dim() == 2 && qkv.size(1) == heads * D, "norm_rope_kv_write: qkv width");
+  TORCH_CHECK(D > 0 && D <= 256, "norm_rope_kv_write: head size must be at most 256");
+  const int64_t T = qkv.size(0);
+  TORCH_CHECK(q_out.dim() == 2 && q_out.size(0) == T && q_out.size(1) == nq * D, "norm_rope_kv_write: q_out shape");
+  TORCH_CHECK(positions.numel() >= T && token_seq.numel() >= T && block_tables.dim() == 2,
+              "norm_rope_kv_write: the batch arrays disagree");
+  TORCH_CHECK(qw.has_value() == kw.has_value() && cos.has_value() == sin.has_value() &&
+                  k_pages.has_value() == v_pages.has_value(),
+              "norm_rope_kv_write: weights, tables and pages come in pairs");
+  if (cos) {
+    check_f32(*cos, "cos");
+    check_f32(*sin, "sin");
+    TORCH_CHECK(cos->dim() == 2 && cos->size(1) == D / 2 && sin->sizes() == cos->sizes() && D % 2 == 0,
+                "norm_rope_kv_write: cos and sin must be [positions, head_dim / 2]");
+  }
+  void *kp = nullptr, *vp = nullptr;
+  if (k_pages) {
+    check_cuda(*k_pages, "k_pages");
+    check_cuda(*v_pages, "v_pages");
+    TORCH_CHECK(k_pages->scalar_type() == q_out.scalar_type() && v_pages->scalar_type() == q_out.scalar_type() &&
+                    k_pages->dim() == 4 && k_pages->size(1) == nk && k_pages->size(2) == page_tokens &&
+                    k_pages->size(3) == D && v_pages->sizes() == k_pages->sizes(),
+                "norm_rope_kv_write: pages must be [pages, kv_heads, page_tokens, head_dim] of q_out's dtype");
+    kp = k_pages->data_ptr();
+    vp = v_pages->data_ptr();
+  }
+  done(lse_norm_rope_kv_write(qkv.data_ptr<float>(), q_out.data_ptr(), out_code(q_out, "q_out"), (int)T, (int)nq,
+                              (int)nk, (int)D, v_from_k ? 1 : 0, opt_f32(qw, D, "q weight"), opt_f32(kw, D, "k weight"),
+                              (float)eps, positions.data_ptr<int>(), token_seq.data_ptr<int>(),
+                              cos ? cos->data_ptr<float>() : nullptr, sin ? sin->data_ptr<float>() : nullptr, kp, vp,
+                              block_tables.data_ptr<int>(), (int)block_tables.size(1), (int)page_tokens, stream()),
+       "norm_rope_kv_write");
+}
+
+void decay_linear_attention(const Tensor& proj, Tensor& out, Tensor& state, const Tensor& decay, const Tensor& cu_q,
+                            const Tensor& ctx_lens, const Tensor& slots, int64_t H, int64_t dk, int64_t dv,
+                            const OptTensor& cos, const OptTensor& sin, bool silu, double key_scale) {
+  check_f32(proj, "proj");
+  check_f32(out, "out");
+  check_f32(state, "state");
+  check_f32(decay, "decay");
+  check_i32(cu_q, "cu_q");
+  check_i32(ctx_lens, "ctx_lens");
+  check_i32(slots, "slots");
+  TORCH_CHECK(proj.dim() == 2 && proj.size(1) >= 2 * H * dk + H * dv, "decay_linear_attention: proj is too narrow");
+  TORCH_CHECK(out.dim() == 2 && out.size(0) == proj.size(0) && out.size(1) == H * dv,
+              "decay_linear_attention: out must be [T, heads * value_dim]");
+  TORCH_CHECK(state.dim() == 4 && state.size(1) == H && state.size(2) == dv && state.size(3) == dk,
+              "decay_linear_attention: state must be [slots, heads, value_dim, key_dim]");
+  TORCH_CHECK(decay.numel() == H && cu_q.numel() == ctx_lens.numel() + 1 && slots.numel() >= ctx_lens.numel(),
+              "decay_linear_attention: per-head or per-sequence arrays disagree");
+  TORCH_CHECK(dk > 0 && dk <= 256 && dv > 0, "decay_linear_attention: key size must be at most 256");
+  TORCH_CHECK(cos.has_value() == sin.has_value(), "decay_linear_attention: cos and sin go together");
+  int rot = 0;
+  if (cos) {
+    check_f32(*cos, "cos");
+    check_f32(*sin, "sin");
+    TORCH_CHECK(cos->dim() == 2 && sin->sizes() == cos->sizes() && 2 * cos->size(1) <= dk,
+                "decay_linear_attention: cos and sin must be [positions, rotated dims / 2]");
+    rot = 2 * (int)cos->size(1);
+  }
+  done(lse_decay_linear_attention(proj.data_ptr<float>(), proj.size(1), out.data_ptr<float>(), state.data_ptr<float>(),
+                                  decay.data_ptr<float>(), cu_q.data_ptr<int>(), ctx_lens.data_ptr<int>(),
+                                  slots.data_ptr<int>(), (int)ctx_lens.numel(), (int)H, (int)dk, (int)dv,
+                                  cos ? cos->data_ptr<float>() : nullptr, sin ? sin->data_ptr<float>() : nullptr, rot,
+                                  silu ? 1 : 0, (float)key_scale, stream()),
+       "decay_linear_attention");
 }
 
 bool attention_takes_sums(int64_t D, bool bf16, int64_t num_heads, int64_t num_kv_heads) {
@@ -575,6 +772,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attention_scratch_floats", &attention_scratch_floats);
   m.def("attention_decode_blocks_per_sm", &attention_decode_blocks_per_sm);
   m.def("paged_attention", &paged_attention);
+  m.def("cast_f32", &cast_f32);
+  m.def("token_shift", &token_shift);
+  m.def("rmsnorm_add", &rmsnorm_add);
+  m.def("mix_normed", &mix_normed);
+  m.def("gated_group_norm", &gated_group_norm);
+  m.def("norm_rope_kv_write", &norm_rope_kv_write);
+  m.def("decay_linear_attention", &decay_linear_attention);
   m.def("paged_attention_from_sums", &paged_attention_from_sums);
   m.def("attention_takes_sums", &attention_takes_sums);
   m.def("sample", &sample, py::arg("logits"), py::arg("temperature"), py::arg("top_k"), py::arg("top_p"),

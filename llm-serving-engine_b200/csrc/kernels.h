@@ -106,4 +106,55 @@ int lse_apply_penalties_dense(float* logits, int V, const int* row, const int* s
                               const int* state, int n, cudaStream_t stream);
 int lse_ban_tokens(float* logits, int V, const int* row, const int* token, int n,
                    cudaStream_t stream);
+
+// ---- parts with a running state per request, and blocks that norm a branch's output
+// (state_mixers.cu). A sequence whose first row of the step is at position 0 (ctx_lens - rows
+// == 0) starts from a zero state, whatever its slot holds.
+
+// out = x in out_dtype
+int lse_cast(const float* x, void* out, int out_dtype, long long n, cudaStream_t stream);
+
+// out[t] = x[t] + (x[t-1] - x[t]) * mix, with x[t-1] from state[slots[seq]] for a sequence's first
+// row; afterwards state[slots[seq]] = the sequence's last row of x.   x float32 [T, W]
+int lse_token_shift(const float* x, const float* mix, float* state, void* out, int out_dtype,
+                    const int* token_seq, const int* cu_q, const int* ctx_lens, const int* slots,
+                    int T, int W, cudaStream_t stream);
+
+// y = a, or with wa: ca * wa * a / rms(a) (+ cb * wb * b / rms(b) if b); x += w * y / rms(y);
+// out (may be null) = the new x in out_dtype. rms(v) = sqrt(mean(v^2) + eps), eps_in for a and b.
+int lse_rmsnorm_add(float* x, const float* a, const float* b, const float* wa, const float* wb,
+                    float ca, float cb, float eps_in, const float* w, float eps, void* out,
+                    int out_dtype, int T, int H, cudaStream_t stream);
+// out = ca * wa * a / rms(a) (+ cb * wb * b / rms(b) if b)
+int lse_mix_normed(const float* a, const float* b, const float* wa, const float* wb, float ca,
+                   float cb, float eps, float* out, int T, int H, cudaStream_t stream);
+
+// out[t, g*group + i] = o[t, g*group + i] / rms(o[t, group g]) * weight[g*group + i] (if weight)
+//                       * act(gate[t*gate_stride + g*group + i]),  act = silu or (sigmoid != 0) sigmoid
+int lse_gated_group_norm(const float* o, const float* gate, long long gate_stride, int T, int N,
+                         int group, const float* weight, float eps, int sigmoid, void* out,
+                         int out_dtype, cudaStream_t stream);
+
+// qkv float32 [T, (nq + nk + (v_from_k ? 0 : nk)) * D]. q and k heads: divided by their root mean
+// square and multiplied by qw / kw [D] (if given), then rotated (cos/sin [positions, D/2], if
+// given). q goes to q_out [T, nq*D] of `dtype`; k into k_pages; v (the value heads, or with
+// v_from_k the key heads as projected, before norm and rotation) into v_pages. Pages
+// [pages, nk, page_tokens, D] of `dtype`, or both null when the layer only reads. D <= 256.
+int lse_norm_rope_kv_write(const float* qkv, void* q_out, int dtype, int T, int nq, int nk, int D,
+                           int v_from_k, const float* qw, const float* kw, float eps,
+                           const int* positions, const int* token_seq, const float* cos,
+                           const float* sin, void* k_pages, void* v_pages, const int* block_tables,
+                           int table_stride, int page_tokens, cudaStream_t stream);
+
+// Linear attention with a decay per head, token by token in float32:
+//   S_t = decay[h] * S_{t-1} + k_t v_t^T,  out_t = S_t^T q_t
+// proj [T, stride]: per row q (H*dk) | k (H*dk) | v (H*dv) | anything else. silu != 0: silu on q,
+// k and v. The first `rot` dims of q and k are rotated (pairs (i, i + rot/2), cos/sin
+// [positions, rot/2]); k is then multiplied by key_scale. state [slots, H, dv, dk] float32.
+// dk <= 256.
+int lse_decay_linear_attention(const float* proj, long long stride, float* out, float* state,
+                               const float* decay, const int* cu_q, const int* ctx_lens,
+                               const int* slots, int num_seqs, int H, int dk, int dv,
+                               const float* cos, const float* sin, int rot, int silu,
+                               float key_scale, cudaStream_t stream);
 }

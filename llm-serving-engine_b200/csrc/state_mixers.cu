@@ -1,0 +1,499 @@
+// Kernels of the parts that keep a running state per request, and of blocks that norm a branch's
+// output: token shift, linear attention with a decay per head, the grouped norm with a gate that
+// follows it, query/key norm with the key/value page write, and "x += norm(branch)".
+// All arithmetic is float32; values are rounded once when they are stored in the compute dtype.
+//
+// A request's state lives in row state_slots[seq] of a [slots, ...] float32 tensor. A sequence
+// whose first row of this step is at position 0 starts from zeros, whatever its slot holds.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lse {
+
+#define LSE_CHECK_LAUNCH() (cudaPeekAtLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED)
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+
+// ------------------------------------------------------------------------------------ cast
+template <typename TO>
+__global__ void cast_kernel(const float* __restrict__ x, TO* __restrict__ out, long long n) {
+  pdl_trigger();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = Num<TO>::from_float(x[i]);
+}
+
+// ------------------------------------------------------------------------------------ token shift
+// One block per row. The block of a sequence's first row is the only one that touches the
+// sequence's state: each of its threads reads the old value of its elements and then stores the
+// sequence's last row of this step there.
+template <typename TO>
+__global__ void token_shift_kernel(const float* __restrict__ x, const float* __restrict__ mix,
+                                   float* state, TO* __restrict__ out,
+                                   const int* __restrict__ token_seq, const int* __restrict__ cu_q,
+                                   const int* __restrict__ ctx_lens, const int* __restrict__ slots,
+                                   int W) {
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int s = token_seq[t];
+  const int r0 = cu_q[s], r1 = cu_q[s + 1];
+  const bool first = (t == r0);
+  const bool from_zero = first && (ctx_lens[s] - (r1 - r0) == 0);
+  float* st = state + (size_t)slots[s] * W;
+  pdl_wait();
+  const float* cur = x + (size_t)t * W;
+  const float* prev = first ? st : cur - W;
+  const float* last = x + (size_t)(r1 - 1) * W;
+  TO* o = out + (size_t)t * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float c = cur[i];
+    const float p = from_zero ? 0.f : prev[i];
+    if (first) st[i] = last[i];
+    o[i] = Num<TO>::from_float(c + (p - c) * mix[i]);
+  }
+}
+
+// ------------------------------------------------------------------------------------ x += norm(branch)
+// One block per row. y = a, or, with inner weights, ca * wa * a / rms(a) (+ cb * wb * b / rms(b));
+// then x += w * y / rms(y), and out = x in the compute dtype if out is given. y is recomputed
+// in the last pass rather than kept: the row's second read comes from cache.
+template <typename TO>
+__global__ void rmsnorm_add_kernel(float* __restrict__ x, const float* __restrict__ a,
+                                   const float* __restrict__ b, const float* __restrict__ wa,
+                                   const float* __restrict__ wb, float ca, float cb, float eps_in,
+                                   const float* __restrict__ w, float eps, TO* __restrict__ out,
+                                   int H) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
+  const size_t row = (size_t)blockIdx.x * H;
+  const float* ar = a + row;
+  const float* br = b ? b + row : nullptr;
+  float inv_a = 1.f, inv_b = 1.f;
+  if (wa) {
+    float sa = 0.f, sb = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      const float va = ar[i];
+      sa += va * va;
+      if (br) {
+        const float vb = br[i];
+        sb += vb * vb;
+      }
+    }
+    sa = block_sum(sa, scratch);
+    inv_a = ca * rsqrtf(sa / (float)H + eps_in);
+    if (br) {
+      sb = block_sum(sb, scratch);
+      inv_b = cb * rsqrtf(sb / (float)H + eps_in);
+    }
+  }
+  auto y_at = [&](int i) -> float {
+    if (!wa) return ar[i];
+    float y = ar[i] * inv_a * wa[i];
+    if (br) y += br[i] * inv_b * wb[i];
+    return y;
+  };
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float y = y_at(i);
+    ss += y * y;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  float* xr = x + row;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = xr[i] + y_at(i) * inv * w[i];
+    xr[i] = v;
+    if (out) out[row + i] = Num<TO>::from_float(v);
+  }
+}
+
+// out = ca * wa * a / rms(a) + cb * wb * b / rms(b)   (b may be null)
+__global__ void mix_normed_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                  const float* __restrict__ wa, const float* __restrict__ wb,
+                                  float ca, float cb, float eps, float* __restrict__ out, int H) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
+  const size_t row = (size_t)blockIdx.x * H;
+  float sa = 0.f, sb = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    sa += a[row + i] * a[row + i];
+    if (b) sb += b[row + i] * b[row + i];
+  }
+  sa = block_sum(sa, scratch);
+  const float inv_a = ca * rsqrtf(sa / (float)H + eps);
+  float inv_b = 0.f;
+  if (b) {
+    sb = block_sum(sb, scratch);
+    inv_b = cb * rsqrtf(sb / (float)H + eps);
+  }
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float y = a[row + i] * inv_a * wa[i];
+    if (b) y += b[row + i] * inv_b * wb[i];
+    out[row + i] = y;
+  }
+}
+
+// ------------------------------------------------------------------------------------ grouped norm with a gate
+// out[t, g*group + i] = o / rms(o over the group) * weight * act(gate); one block per (row, group).
+template <typename TO>
+__global__ void gated_group_norm_kernel(const float* __restrict__ o, const float* __restrict__ gate,
+                                        long long gate_stride, int N, int group,
+                                        const float* __restrict__ weight, float eps, int sigmoid,
+                                        TO* __restrict__ out) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, g = blockIdx.y;
+  const float* orow = o + (size_t)t * N + (size_t)g * group;
+  const float* grow = gate + (size_t)t * gate_stride + (size_t)g * group;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < group; i += blockDim.x) ss += orow[i] * orow[i];
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)group + eps);
+  for (int i = threadIdx.x; i < group; i += blockDim.x) {
+    float y = orow[i] * inv;
+    if (weight) y *= weight[g * group + i];
+    const float z = grow[i];
+    y *= sigmoid ? sigmoid_f(z) : silu_f(z);
+    out[(size_t)t * N + (size_t)g * group + i] = Num<TO>::from_float(y);
+  }
+}
+
+// ------------------------------------------------------------------------------------ q/k norm, rotation, page write
+// One warp per (token, head) of the projection's heads: nq query heads, nk key heads, then nk
+// value heads unless the values are the keys as projected. D <= 256.
+constexpr int NRW_WARPS = 4;
+template <typename T>
+__global__ void norm_rope_kv_write_kernel(const float* __restrict__ qkv, T* __restrict__ q_out,
+                                          int nq, int nk, int D, int v_from_k,
+                                          const float* __restrict__ qw, const float* __restrict__ kw,
+                                          float eps, const int* __restrict__ positions,
+                                          const int* __restrict__ token_seq,
+                                          const float* __restrict__ cos, const float* __restrict__ sin,
+                                          T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                          const int* __restrict__ block_tables, int table_stride,
+                                          int page_tokens) {
+  __shared__ float buf[NRW_WARPS][256];
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const int nv = v_from_k ? 0 : nk;
+  const int hs = blockIdx.y * NRW_WARPS + warp;
+  if (hs >= nq + nk + nv) return;
+  const float* src = qkv + (size_t)t * (nq + nk + nv) * D + (size_t)hs * D;
+  const int pos = positions[t];
+  size_t page_base = 0;
+  if (hs >= nq) {
+    const int pi = pos / page_tokens, off = pos - pi * page_tokens;
+    const int page = block_tables[(size_t)token_seq[t] * table_stride + pi];
+    const int kvh = hs < nq + nk ? hs - nq : hs - nq - nk;
+    page_base = (((size_t)page * nk + kvh) * page_tokens + off) * D;
+  }
+  float v[8];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const int i = lane + 32 * c;
+    v[c] = i < D ? src[i] : 0.f;
+    ss += v[c] * v[c];
+  }
+  if (hs >= nq + nk) {  // a value head: stored as projected
+    if (v_pages)
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const int i = lane + 32 * c;
+        if (i < D) v_pages[page_base + i] = Num<T>::from_float(v[c]);
+      }
+    return;
+  }
+  const bool is_q = hs < nq;
+  if (!is_q && v_from_k && v_pages) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int i = lane + 32 * c;
+      if (i < D) v_pages[page_base + i] = Num<T>::from_float(v[c]);
+    }
+  }
+  const float* w = is_q ? qw : kw;
+  if (w) {
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int i = lane + 32 * c;
+      if (i < D) v[c] = v[c] * inv * w[i];
+    }
+  }
+  if (cos) {
+    const int half = D / 2;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int i = lane + 32 * c;
+      if (i < D) buf[warp][i] = v[c];
+    }
+    __syncwarp();
+    const float* cr = cos + (size_t)pos * half;
+    const float* sr = sin + (size_t)pos * half;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int i = lane + 32 * c;
+      if (i < half) v[c] = v[c] * cr[i] - buf[warp][i + half] * sr[i];
+      else if (i < D) v[c] = v[c] * cr[i - half] + buf[warp][i - half] * sr[i - half];
+    }
+  }
+  T* dst = is_q ? q_out + (size_t)t * nq * D + (size_t)hs * D : (k_pages ? k_pages + page_base : nullptr);
+  if (dst)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int i = lane + 32 * c;
+      if (i < D) dst[i] = Num<T>::from_float(v[c]);
+    }
+}
+
+// ------------------------------------------------------------------------------------ linear attention with decay
+// S_t = decay * S_{t-1} + k_t v_t^T,  o_t = S_t^T q_t, stepped token by token in float32.
+// One block per (head, slice of CB value columns, sequence); 256 threads. A column of S (key_dim
+// values) is shared by P neighbouring lanes, RPT = 16 rows each, held in registers across the
+// whole portion; the P partial dot products of o are added with shuffles. Columns are
+// independent of one another, so slices of a head's columns run as separate blocks. q, k (after
+// activation, rotation and scaling) and v of TT tokens are staged in shared memory per pass.
+// The state is stored transposed, [slot][head][value_dim][key_dim]: a thread's rows are
+// contiguous there.
+constexpr int LA_RPT = 16, LA_TT = 16, LA_THREADS = 256, LA_PAD = 4;
+
+struct LinAttnArgs {
+  const float* proj;      // [T, stride]: q | k | v | ... per row, heads concatenated
+  long long stride;
+  float* out;             // [T, H * dv]
+  float* state;           // [slots, H, dv, dk]
+  const float* decay;     // [H]
+  const int* cu_q;
+  const int* ctx_lens;
+  const int* slots;
+  const float* cos;       // [positions, rot/2] or null
+  const float* sin;
+  int H, dk, dv, rot, silu;
+  float key_scale;
+  int P, CB;              // lanes per column; columns per block
+};
+
+__global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(const LinAttnArgs a) {
+  extern __shared__ float la_smem[];
+  pdl_trigger();
+  const int P = a.P, CB = a.CB, dk = a.dk, dv = a.dv, H = a.H;
+  const int slices = (dv + CB - 1) / CB;
+  const int h = blockIdx.x / slices, cb = blockIdx.x - h * slices;
+  const int seq = blockIdx.y;
+  const int r0 = a.cu_q[seq], n = a.cu_q[seq + 1] - r0;
+  const int pos0 = a.ctx_lens[seq] - n;
+  const int p = threadIdx.x % P, jl = threadIdx.x / P;
+  const int j = cb * CB + jl;
+  const int ldq = P * (LA_RPT + LA_PAD);
+  float* qs = la_smem;                  // [TT][ldq]
+  float* ks = qs + LA_TT * ldq;         // [TT][ldq]
+  float* vs = ks + LA_TT * ldq;         // [TT][CB]
+  const float decay = a.decay[h];
+  float S[LA_RPT];
+  float* st = a.state + (((size_t)a.slots[seq] * H + h) * dv + (j < dv ? j : 0)) * dk + p * LA_RPT;
+  pdl_wait();
+#pragma unroll
+  for (int r = 0; r < LA_RPT; ++r)
+    S[r] = (pos0 > 0 && j < dv && p * LA_RPT + r < dk) ? st[r] : 0.f;
+  const int half = a.rot / 2;
+  for (int t0 = 0; t0 < n; t0 += LA_TT) {
+    const int tn = min(LA_TT, n - t0);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < tn * P * LA_RPT; idx += LA_THREADS) {
+      const int tt = idx / (P * LA_RPT), i = idx - tt * (P * LA_RPT);
+      float q = 0.f, k = 0.f;
+      if (i < dk) {
+        const float* row = a.proj + (size_t)(r0 + t0 + tt) * a.stride + (size_t)h * dk;
+        const float* krow = row + (size_t)H * dk;
+        q = row[i];
+        k = krow[i];
+        if (a.silu) {
+          q = silu_f(q);
+          k = silu_f(k);
+        }
+        if (i < a.rot) {
+          const int f = i < half ? i : i - half;
+          const size_t at = (size_t)(pos0 + t0 + tt) * half + f;
+          const float c = a.cos[at], s = a.sin[at];
+          const int ip = i < half ? i + half : i - half;
+          float qp = row[ip], kp = krow[ip];
+          if (a.silu) {
+            qp = silu_f(qp);
+            kp = silu_f(kp);
+          }
+          q = i < half ? q * c - qp * s : q * c + qp * s;
+          k = i < half ? k * c - kp * s : k * c + kp * s;
+        }
+        k *= a.key_scale;
+      }
+      const int at = tt * ldq + (i / LA_RPT) * (LA_RPT + LA_PAD) + (i % LA_RPT);
+      qs[at] = q;
+      ks[at] = k;
+    }
+    for (int idx = threadIdx.x; idx < tn * CB; idx += LA_THREADS) {
+      const int tt = idx / CB, c = idx - tt * CB;
+      float v = 0.f;
+      if (cb * CB + c < dv) {
+        v = a.proj[(size_t)(r0 + t0 + tt) * a.stride + (size_t)2 * H * dk + (size_t)h * dv + cb * CB + c];
+        if (a.silu) v = silu_f(v);
+      }
+      vs[idx] = v;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < tn; ++tt) {
+      const float vj = vs[tt * CB + jl];
+      const float4* q4 = reinterpret_cast<const float4*>(qs + tt * ldq + p * (LA_RPT + LA_PAD));
+      const float4* k4 = reinterpret_cast<const float4*>(ks + tt * ldq + p * (LA_RPT + LA_PAD));
+      float acc = 0.f;
+#pragma unroll
+      for (int r4 = 0; r4 < LA_RPT / 4; ++r4) {
+        const float4 q = q4[r4], k = k4[r4];
+        S[4 * r4 + 0] = fmaf(decay, S[4 * r4 + 0], k.x * vj);
+        S[4 * r4 + 1] = fmaf(decay, S[4 * r4 + 1], k.y * vj);
+        S[4 * r4 + 2] = fmaf(decay, S[4 * r4 + 2], k.z * vj);
+        S[4 * r4 + 3] = fmaf(decay, S[4 * r4 + 3], k.w * vj);
+        acc = fmaf(S[4 * r4 + 0], q.x, acc);
+        acc = fmaf(S[4 * r4 + 1], q.y, acc);
+        acc = fmaf(S[4 * r4 + 2], q.z, acc);
+        acc = fmaf(S[4 * r4 + 3], q.w, acc);
+      }
+      for (int o = P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (p == 0 && j < dv) a.out[(size_t)(r0 + t0 + tt) * ((size_t)H * dv) + (size_t)h * dv + j] = acc;
+    }
+  }
+  if (j < dv)
+#pragma unroll
+    for (int r = 0; r < LA_RPT; ++r)
+      if (p * LA_RPT + r < dk) st[r] = S[r];
+}
+
+static int pow2_at_least(int n) {
+  int p = 1;
+  while (p < n) p <<= 1;
+  return p;
+}
+
+}  // namespace lse
+
+using namespace lse;
+
+extern "C" int lse_cast(const float* x, void* out, int out_dtype, long long n, cudaStream_t stream) {
+  if (n <= 0) return LSE_OK;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (out_dtype == LSE_BF16) launch(cast_kernel<bf16>, blocks, 256, 0, stream, x, (bf16*)out, n);
+  else if (out_dtype == LSE_F32) launch(cast_kernel<float>, blocks, 256, 0, stream, x, (float*)out, n);
+  else return LSE_BAD_ARGUMENT;
+  return LSE_CHECK_LAUNCH();
+}
+
+extern "C" int lse_token_shift(const float* x, const float* mix, float* state, void* out, int out_dtype,
+                               const int* token_seq, const int* cu_q, const int* ctx_lens,
+                               const int* slots, int T, int W, cudaStream_t stream) {
+  if (T <= 0) return LSE_OK;
+  const int threads = W >= 1024 ? 256 : 128;
+  if (out_dtype == LSE_BF16)
+    launch(token_shift_kernel<bf16>, T, threads, 0, stream, x, mix, state, (bf16*)out, token_seq, cu_q,
+           ctx_lens, slots, W);
+  else if (out_dtype == LSE_F32)
+    launch(token_shift_kernel<float>, T, threads, 0, stream, x, mix, state, (float*)out, token_seq, cu_q,
+           ctx_lens, slots, W);
+  else return LSE_BAD_ARGUMENT;
+  return LSE_CHECK_LAUNCH();
+}
+
+extern "C" int lse_rmsnorm_add(float* x, const float* a, const float* b, const float* wa, const float* wb,
+                               float ca, float cb, float eps_in, const float* w, float eps, void* out,
+                               int out_dtype, int T, int H, cudaStream_t stream) {
+  if (T <= 0) return LSE_OK;
+  if (!x || !a || !w || (b && !wa) || (wa && b && !wb)) return LSE_BAD_ARGUMENT;
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  if (out && out_dtype == LSE_BF16)
+    launch(rmsnorm_add_kernel<bf16>, T, threads, 0, stream, x, a, b, wa, wb, ca, cb, eps_in, w, eps,
+           (bf16*)out, H);
+  else if (!out || out_dtype == LSE_F32)
+    launch(rmsnorm_add_kernel<float>, T, threads, 0, stream, x, a, b, wa, wb, ca, cb, eps_in, w, eps,
+           (float*)out, H);
+  else return LSE_BAD_ARGUMENT;
+  return LSE_CHECK_LAUNCH();
+}
+
+extern "C" int lse_mix_normed(const float* a, const float* b, const float* wa, const float* wb, float ca,
+                              float cb, float eps, float* out, int T, int H, cudaStream_t stream) {
+  if (T <= 0) return LSE_OK;
+  if (!a || !wa || (b && !wb) || !out) return LSE_BAD_ARGUMENT;
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  launch(mix_normed_kernel, T, threads, 0, stream, a, b, wa, wb, ca, cb, eps, out, H);
+  return LSE_CHECK_LAUNCH();
+}
+
+extern "C" int lse_gated_group_norm(const float* o, const float* gate, long long gate_stride, int T, int N,
+                                    int group, const float* weight, float eps, int sigmoid, void* out,
+                                    int out_dtype, cudaStream_t stream) {
+  if (T <= 0) return LSE_OK;
+  if (group <= 0 || N % group || N / group > 65535) return LSE_BAD_ARGUMENT;
+  const int threads = group >= 1024 ? 256 : (group >= 128 ? 128 : (group > 32 ? 64 : 32));
+  dim3 grid(T, N / group);
+  if (out_dtype == LSE_BF16)
+    launch(gated_group_norm_kernel<bf16>, grid, threads, 0, stream, o, gate, gate_stride, N, group, weight,
+           eps, sigmoid, (bf16*)out);
+  else if (out_dtype == LSE_F32)
+    launch(gated_group_norm_kernel<float>, grid, threads, 0, stream, o, gate, gate_stride, N, group, weight,
+           eps, sigmoid, (float*)out);
+  else return LSE_BAD_ARGUMENT;
+  return LSE_CHECK_LAUNCH();
+}
+
+extern "C" int lse_norm_rope_kv_write(const float* qkv, void* q_out, int dtype, int T, int nq, int nk, int D,
+                                      int v_from_k, const float* qw, const float* kw, float eps,
+                                      const int* positions, const int* token_seq, const float* cos,
+                                      const float* sin, void* k_pages, void* v_pages,
+                                      const int* block_tables, int table_stride, int page_tokens,
+                                      cudaStream_t stream) {
+  if (T <= 0) return LSE_OK;
+  if (D <= 0 || D > 256 || (cos && D % 2) || (!qw != !kw) || (!cos != !sin) || (!k_pages != !v_pages) ||
+      page_tokens <= 0)
+    return LSE_BAD_ARGUMENT;
+  const int heads = nq + nk + (v_from_k ? 0 : nk);
+  dim3 grid(T, (heads + NRW_WARPS - 1) / NRW_WARPS);
+  if (grid.y > 65535) return LSE_BAD_ARGUMENT;
+  if (dtype == LSE_BF16)
+    launch(norm_rope_kv_write_kernel<bf16>, grid, NRW_WARPS * 32, 0, stream, qkv, (bf16*)q_out, nq, nk, D,
+           v_from_k, qw, kw, eps, positions, token_seq, cos, sin, (bf16*)k_pages, (bf16*)v_pages,
+           block_tables, table_stride, page_tokens);
+  else if (dtype == LSE_F32)
+    launch(norm_rope_kv_write_kernel<float>, grid, NRW_WARPS * 32, 0, stream, qkv, (float*)q_out, nq, nk, D,
+           v_from_k, qw, kw, eps, positions, token_seq, cos, sin, (float*)k_pages, (float*)v_pages,
+           block_tables, table_stride, page_tokens);
+  else return LSE_BAD_ARGUMENT;
+  return LSE_CHECK_LAUNCH();
+}
+
+extern "C" int lse_decay_linear_attention(const float* proj, long long stride, float* out, float* state,
+                                          const float* decay, const int* cu_q, const int* ctx_lens,
+                                          const int* slots, int num_seqs, int H, int dk, int dv,
+                                          const float* cos, const float* sin, int rot, int silu,
+                                          float key_scale, cudaStream_t stream) {
+  if (num_seqs <= 0) return LSE_OK;
+  if (H <= 0 || dk <= 0 || dv <= 0 || dk > 256 || rot < 0 || rot > dk || rot % 2 || (rot && (!cos || !sin)) ||
+      num_seqs > 65535)
+    return LSE_BAD_ARGUMENT;
+  LinAttnArgs a;
+  a.proj = proj; a.stride = stride; a.out = out; a.state = state; a.decay = decay; a.cu_q = cu_q;
+  a.ctx_lens = ctx_lens; a.slots = slots; a.cos = cos; a.sin = sin; a.H = H; a.dk = dk; a.dv = dv;
+  a.rot = rot; a.silu = silu; a.key_scale = key_scale;
+  a.P = pow2_at_least((dk + LA_RPT - 1) / LA_RPT);
+  a.CB = LA_THREADS / a.P;
+  const int slices = (dv + a.CB - 1) / a.CB;
+  const size_t smem = ((size_t)2 * LA_TT * a.P * (LA_RPT + LA_PAD) + (size_t)LA_TT * a.CB) * sizeof(float);
+  dim3 grid(H * slices, num_seqs);
+  launch(decay_linear_attention_kernel, grid, LA_THREADS, smem, stream, a);
+  return LSE_CHECK_LAUNCH();
+}

@@ -372,7 +372,10 @@ class CudaOps:
         return choose_decode_splits(num_decode * num_kv_heads, max_ctx, self.num_sms, self.decode_blocks_per_sm)
 
     def paged_attention(self, q, *, num_heads, num_kv_heads, head_dim, scale, window, k_pages,
-                        v_pages, block_tables, page_tokens, step, plan):
+                        v_pages, block_tables, page_tokens, step, plan, head_scale=None, slopes=None,
+                        chunk=0):
+        """``head_scale`` / ``slopes`` (float32 ``[heads]``) and ``chunk``: a factor per head on the
+        score, ``slope_h * (i - j)`` taken off it, and keys limited to the query's chunk."""
         out = torch.empty(q.shape[0], num_heads * head_dim, dtype=q.dtype, device=q.device)
         n_tiles = int(plan["tiles"].shape[0])
         n_dec = int(plan["decode_seqs"].shape[0])
@@ -387,9 +390,84 @@ class CudaOps:
             int(window), block_tables, step.ctx_lens, step.cu_q,
             plan["tiles"] if n_tiles else None, n_tiles,
             plan["decode_seqs"] if n_dec else None, n_dec, splits, scratch,
-            self.attention_kernel,
+            self.attention_kernel, head_scale, slopes, int(chunk),
         )
         self.launches += (1 if n_tiles else 0) + (1 if n_dec else 0)
+        return out
+
+    def norm_rope_kv_write(self, qkv, *, num_heads, num_kv_heads, head_dim, values_are_keys, q_weight,
+                           k_weight, eps, positions, token_seq, cos, sin, k_pages, v_pages,
+                           block_tables, page_tokens, out_dtype):
+        """Head-wise RMS norm of q and k (if weights are given), rotation (if tables are given),
+        key/value page write; returns the queries ``[T, heads * head_dim]`` in ``out_dtype``.
+        ``qkv`` is the float32 projection; with ``values_are_keys`` it has no value heads and a
+        token's value is its key as projected."""
+        q = torch.empty(qkv.shape[0], num_heads * head_dim, dtype=out_dtype, device=qkv.device)
+        self.ext.norm_rope_kv_write(qkv, q, num_heads, num_kv_heads, head_dim, bool(values_are_keys),
+                                    q_weight, k_weight, float(eps), positions, token_seq, cos, sin,
+                                    k_pages, v_pages, block_tables, int(page_tokens))
+        self.launches += 1
+        return q
+
+    # ------------------------------------------------------------------ branch-norm blocks, state mixers
+    def cast(self, x, dtype):
+        """The float32 residual stream in the compute dtype (itself, if that is float32)."""
+        if x.dtype == dtype:
+            return x
+        out = torch.empty(x.shape, dtype=dtype, device=x.device)
+        self.ext.cast_f32(x, out)
+        self.launches += 1
+        return out
+
+    def token_shift(self, x, mix, state, step, out_dtype):
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        self.ext.token_shift(x, mix, state, out, step.token_seq, step.cu_q, step.ctx_lens, step.state_slots)
+        self.launches += 1
+        return out
+
+    @staticmethod
+    def _two_branches(branches, weights, coefficients):
+        if not 1 <= len(branches) <= 2:
+            raise NotImplementedError("the kernels norm and sum one or two branches")
+        b = branches[1] if len(branches) == 2 else None
+        wb = weights[1] if len(branches) == 2 else None
+        cb = coefficients[1] if len(branches) == 2 else 0.0
+        return branches[0], b, weights[0], wb, float(coefficients[0]), float(cb)
+
+    def mix_normed(self, branches, weights, coefficients, eps):
+        a, b, wa, wb, ca, cb = self._two_branches(branches, weights, coefficients)
+        out = torch.empty_like(a)
+        self.ext.mix_normed(a, b, wa, wb, ca, cb, float(eps), out)
+        self.launches += 1
+        return out
+
+    def rmsnorm_add(self, x, branch, weight, eps, out_dtype=None):
+        """``x += weight * y / rms(y)`` with ``y`` the branch (a float32 tensor, or a
+        ``BranchMix`` whose members are normed and summed in the same launch); returns the new
+        ``x`` in ``out_dtype`` unless that is None."""
+        out = None if out_dtype is None else torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        if hasattr(branch, "branches"):
+            a, b, wa, wb, ca, cb = self._two_branches(branch.branches, branch.weights, branch.coefficients)
+            self.ext.rmsnorm_add(x, a, b, wa, wb, ca, cb, float(branch.eps), weight, float(eps), out)
+        else:
+            self.ext.rmsnorm_add(x, branch, None, None, None, 1.0, 0.0, 0.0, weight, float(eps), out)
+        self.launches += 1
+        return out
+
+    def decay_linear_attention(self, proj, *, num_heads, key_dim, value_dim, decay, state, step,
+                               activation, key_scale, cos, sin):
+        out = torch.empty(proj.shape[0], num_heads * value_dim, dtype=torch.float32, device=proj.device)
+        self.ext.decay_linear_attention(proj, out, state, decay, step.cu_q, step.ctx_lens, step.state_slots,
+                                        num_heads, key_dim, value_dim, cos, sin, activation == "silu",
+                                        float(key_scale))
+        self.launches += 1
+        return out
+
+    def gated_group_norm(self, o, proj, *, gate_offset, group, weight, eps, gate_activation, out_dtype):
+        out = torch.empty(o.shape, dtype=out_dtype, device=o.device)
+        self.ext.gated_group_norm(o, proj, int(gate_offset), int(group), weight, float(eps),
+                                  gate_activation == "sigmoid", out)
+        self.launches += 1
         return out
 
     # ------------------------------------------------------------------ sampling
