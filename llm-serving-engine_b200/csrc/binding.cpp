@@ -494,8 +494,9 @@ void norm_rope_kv_write(const Tensor& qkv, Tensor& q_out, int64_t nq, int64_t nk
                         const OptTensor& qw, const OptTensor& kw, double eps, const Tensor& positions,
                         const Tensor& token_seq, const OptTensor& cos, const OptTensor& sin,
                         const OptTensor& k_pages, const OptTensor& v_pages, const Tensor& block_tables,
-                        int64_t page_tokens) {
+                        int64_t page_tokens, int64_t norm_dim) {
   check_f32(qkv, "qkv");
+  TORCH_CHECK(norm_dim > 0 && norm_dim <= D, "norm_rope_kv_write: norm_dim must lie in 1..head_dim");
   check_cuda(q_out, "q_out");
   check_i32(positions, "positions");
   check_i32(token_seq, "token_seq");
@@ -531,7 +532,8 @@ void norm_rope_kv_write(const Tensor& qkv, Tensor& q_out, int64_t nq, int64_t nk
                               (int)nk, (int)D, v_from_k ? 1 : 0, opt_f32(qw, D, "q weight"), opt_f32(kw, D, "k weight"),
                               (float)eps, positions.data_ptr<int>(), token_seq.data_ptr<int>(),
                               cos ? cos->data_ptr<float>() : nullptr, sin ? sin->data_ptr<float>() : nullptr, kp, vp,
-                              block_tables.data_ptr<int>(), (int)block_tables.size(1), (int)page_tokens, stream()),
+                              block_tables.data_ptr<int>(), (int)block_tables.size(1), (int)page_tokens,
+                              (int)norm_dim, stream()),
        "norm_rope_kv_write");
 }
 

@@ -140,11 +140,12 @@ int lse_gated_group_norm(const float* o, const float* gate, long long gate_strid
 // given). q goes to q_out [T, nq*D] of `dtype`; k into k_pages; v (the value heads, or with
 // v_from_k the key heads as projected, before norm and rotation) into v_pages. Pages
 // [pages, nk, page_tokens, D] of `dtype`, or both null when the layer only reads. D <= 256.
+// norm_dim: the mean of the norm is taken over this many dims (the rest of a head is zero padding).
 int lse_norm_rope_kv_write(const float* qkv, void* q_out, int dtype, int T, int nq, int nk, int D,
                            int v_from_k, const float* qw, const float* kw, float eps,
                            const int* positions, const int* token_seq, const float* cos,
                            const float* sin, void* k_pages, void* v_pages, const int* block_tables,
-                           int table_stride, int page_tokens, cudaStream_t stream);
+                           int table_stride, int page_tokens, int norm_dim, cudaStream_t stream);
 
 // Linear attention with a decay per head, token by token in float32:
 //   S_t = decay[h] * S_{t-1} + k_t v_t^T,  out_t = S_t^T q_t

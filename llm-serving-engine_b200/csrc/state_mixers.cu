@@ -175,7 +175,7 @@ __global__ void norm_rope_kv_write_kernel(const float* __restrict__ qkv, T* __re
                                           const float* __restrict__ cos, const float* __restrict__ sin,
                                           T* __restrict__ k_pages, T* __restrict__ v_pages,
                                           const int* __restrict__ block_tables, int table_stride,
-                                          int page_tokens) {
+                                          int page_tokens, int norm_dim) {
   __shared__ float buf[NRW_WARPS][256];
   pdl_trigger();
   pdl_wait();
@@ -221,7 +221,7 @@ __global__ void norm_rope_kv_write_kernel(const float* __restrict__ qkv, T* __re
   const float* w = is_q ? qw : kw;
   if (w) {
     ss = warp_sum(ss);
-    const float inv = rsqrtf(ss / (float)D + eps);
+    const float inv = rsqrtf(ss / (float)norm_dim + eps);
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
       const int i = lane + 32 * c;
@@ -456,7 +456,7 @@ extern "C" int lse_norm_rope_kv_write(const float* qkv, void* q_out, int dtype, 
                                       const int* positions, const int* token_seq, const float* cos,
                                       const float* sin, void* k_pages, void* v_pages,
                                       const int* block_tables, int table_stride, int page_tokens,
-                                      cudaStream_t stream) {
+                                      int norm_dim, cudaStream_t stream) {
   if (T <= 0) return LSE_OK;
   if (D <= 0 || D > 256 || (cos && D % 2) || (!qw != !kw) || (!cos != !sin) || (!k_pages != !v_pages) ||
       page_tokens <= 0)
@@ -467,11 +467,11 @@ extern "C" int lse_norm_rope_kv_write(const float* qkv, void* q_out, int dtype, 
   if (dtype == LSE_BF16)
     launch(norm_rope_kv_write_kernel<bf16>, grid, NRW_WARPS * 32, 0, stream, qkv, (bf16*)q_out, nq, nk, D,
            v_from_k, qw, kw, eps, positions, token_seq, cos, sin, (bf16*)k_pages, (bf16*)v_pages,
-           block_tables, table_stride, page_tokens);
+           block_tables, table_stride, page_tokens, norm_dim);
   else if (dtype == LSE_F32)
     launch(norm_rope_kv_write_kernel<float>, grid, NRW_WARPS * 32, 0, stream, qkv, (float*)q_out, nq, nk, D,
            v_from_k, qw, kw, eps, positions, token_seq, cos, sin, (float*)k_pages, (float*)v_pages,
-           block_tables, table_stride, page_tokens);
+           block_tables, table_stride, page_tokens, norm_dim);
   else return LSE_BAD_ARGUMENT;
   return LSE_CHECK_LAUNCH();
 }

@@ -140,6 +140,9 @@ class LLMEngine:
         self.last_step = StepStats()
         self.total_steps = 0
         self._pending: _InFlight | None = None  # a step launched ahead, not yet collected
+        # Parts with a running state per request (a recurrence, a token shift) change it for good
+        # in every step, so a step can never be dropped and run again: nothing is launched ahead.
+        self._keeps_running_state = any(getattr(p, "keeps_running_state", False) for p in self.model.parts())
         if cfg.warm_up and self.runner.device.type == "cuda":
             self._warm_up()
 
@@ -297,6 +300,8 @@ class LLMEngine:
     def _launch_ahead(self, cur: "_InFlight"):
         """Launch the step after ``cur`` before ``cur``'s tokens are known, if the batch cannot change."""
         if cur.pending is None or not self.cfg.run_ahead or self.scheduler.waiting:
+            return None
+        if self._keeps_running_state:  # a dropped step would have advanced the survivors' states
             return None
         if not cur.pending.feeds_next:  # sampled outside the graph, or rows in another order
             return None

@@ -397,15 +397,17 @@ class CudaOps:
 
     def norm_rope_kv_write(self, qkv, *, num_heads, num_kv_heads, head_dim, values_are_keys, q_weight,
                            k_weight, eps, positions, token_seq, cos, sin, k_pages, v_pages,
-                           block_tables, page_tokens, out_dtype):
+                           block_tables, page_tokens, out_dtype, norm_dim=None):
         """Head-wise RMS norm of q and k (if weights are given), rotation (if tables are given),
         key/value page write; returns the queries ``[T, heads * head_dim]`` in ``out_dtype``.
         ``qkv`` is the float32 projection; with ``values_are_keys`` it has no value heads and a
-        token's value is its key as projected."""
+        token's value is its key as projected. ``norm_dim``: the number of dims the mean of the
+        norm is taken over, when the trailing dims of a head are zero padding."""
         q = torch.empty(qkv.shape[0], num_heads * head_dim, dtype=out_dtype, device=qkv.device)
         self.ext.norm_rope_kv_write(qkv, q, num_heads, num_kv_heads, head_dim, bool(values_are_keys),
                                     q_weight, k_weight, float(eps), positions, token_seq, cos, sin,
-                                    k_pages, v_pages, block_tables, int(page_tokens))
+                                    k_pages, v_pages, block_tables, int(page_tokens),
+                                    int(norm_dim or head_dim))
         self.launches += 1
         return q
 

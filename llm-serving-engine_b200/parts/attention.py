@@ -67,12 +67,20 @@ class PagedAttention(Mixer):
         # the plain path (fused projection, rotation, cache write and attention) serves none of these
         self.extended = (spec.qk_norm_eps is not None or spec.values_are_keys or spec.head_temperature
                          or spec.distance_slopes is not None or spec.chunk > 0)
+        # The attention kernels take head sizes that are multiples of 16. With the score options on,
+        # any other head size is padded with zeros up to the next one when the weights are bound:
+        # zero dims change no dot product, the norm divides by the true size, and the padded dims
+        # of the output (values are zero there) meet zero columns of the output projection.
+        self.pad = (-spec.head_dim) % 16 if self.extended else 0
+        self.kernel_dim = spec.head_dim + self.pad
+        if self.pad and self.rotary is not None:
+            raise NotImplementedError("a padded head size with rotary positions")
         self.slopes = None
         if spec.distance_slopes is not None:
             if len(spec.distance_slopes) != spec.num_heads:
                 raise ValueError("one distance slope per query head is needed")
             self.slopes = torch.tensor(spec.distance_slopes, dtype=torch.float64).to(torch.float32).to(env.device)
-        env.ops.check_attention_shape(spec.head_dim, env.dtype, spec.num_heads, spec.num_kv_heads)
+        env.ops.check_attention_shape(self.kernel_dim, env.dtype, spec.num_heads, spec.num_kv_heads)
 
     def param_decls(self):
         s = self.spec
@@ -98,30 +106,48 @@ class PagedAttention(Mixer):
         self.q_norm_weight = params.get("q_norm.weight")
         self.k_norm_weight = params.get("k_norm.weight")
         self.temperature = params.get("temperature")
+        if self.pad:
+            s, D, Dp = self.spec, self.spec.head_dim, self.kernel_dim
+            heads = self.qkv_weight.shape[0] // D
+
+            def pad_rows(w):  # [heads * D, ...] -> [heads * Dp, ...], zeros after each head's rows
+                out = w.new_zeros((heads, Dp) + tuple(w.shape[1:]))
+                out[:, :D] = w.view((heads, D) + tuple(w.shape[1:]))
+                return out.view((heads * Dp,) + tuple(w.shape[1:])).contiguous()
+
+            self.qkv_weight = pad_rows(self.qkv_weight)
+            if self.qkv_bias is not None:
+                self.qkv_bias = pad_rows(self.qkv_bias)
+            o = self.o_weight.new_zeros(s.hidden_size, s.num_heads, Dp)
+            o[:, :, :D] = self.o_weight.view(s.hidden_size, s.num_heads, D)
+            self.o_weight = o.view(s.hidden_size, s.num_heads * Dp).contiguous()
+            if self.q_norm_weight is not None:
+                self.q_norm_weight = torch.nn.functional.pad(self.q_norm_weight, (0, self.pad))
+                self.k_norm_weight = torch.nn.functional.pad(self.k_norm_weight, (0, self.pad))
 
     # what the cache manager has to keep for a layer of this kind
     def cache_need(self):
         s = self.spec
-        return PagedKVNeed(s.num_kv_heads, s.head_dim, s.window)
+        return PagedKVNeed(s.num_kv_heads, self.kernel_dim, s.window)
 
     def reserve(self, max_seqs: int) -> None:
         """Allocate kernel scratch for up to ``max_seqs`` single-token sequences in a step."""
         if hasattr(self.ops, "reserve_attention_scratch"):
-            self.ops.reserve_attention_scratch(self.spec.head_dim, max_seqs, self.spec.num_heads)
+            self.ops.reserve_attention_scratch(self.kernel_dim, max_seqs, self.spec.num_heads)
 
     # work lists depend only on the batch, the kernels' tile size and the group's page size
     def plan_key(self):
-        return ("attention", self.env.dtype, self.spec.head_dim)
+        return ("attention", self.env.dtype, self.kernel_dim)
 
     def plan_step(self, host_step, group):
-        return self.ops.attention_plan(host_step, self.env.dtype, self.spec.head_dim)
+        return self.ops.attention_plan(host_step, self.env.dtype, self.kernel_dim)
 
     def plan_rows(self, single: int, portions: int, tokens: int) -> dict[str, int]:
         """Most rows of each work list for a step of ``single`` one-token sequences and ``portions``
         longer ones that hold ``tokens`` tokens together. A captured step has lists of exactly this
         many rows; a shorter list is filled up by repeating its last row (a tile that is computed
         twice writes the same values twice)."""
-        qt = self.ops.attention_q_tile(self.env.dtype, self.spec.head_dim)
+        qt = self.ops.attention_q_tile(self.env.dtype, self.kernel_dim)
         return {"tiles": tokens // qt + portions, "decode_seqs": single}
 
     accepts_residual = True
@@ -162,14 +188,15 @@ class PagedAttention(Mixer):
         s, ops = self.spec, self.ops
         qkv = ops.linear(h, self.qkv_weight, self.qkv_bias, out_dtype=torch.float32)
         q = ops.norm_rope_kv_write(
-            qkv, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,
+            qkv, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=self.kernel_dim,
+            norm_dim=s.head_dim,
             values_are_keys=s.values_are_keys, q_weight=self.q_norm_weight, k_weight=self.k_norm_weight,
             eps=s.qk_norm_eps if s.qk_norm_eps is not None else 0.0,
             positions=step.positions, token_seq=step.token_seq, cos=cos, sin=sin,
             k_pages=cache.k if cache.writes else None, v_pages=cache.v if cache.writes else None,
             block_tables=tables, page_tokens=cache.page_tokens, out_dtype=self.env.dtype)
         return ops.paged_attention(
-            q, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim, scale=s.scale,
+            q, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=self.kernel_dim, scale=s.scale,
             window=s.window, k_pages=cache.k, v_pages=cache.v, block_tables=tables,
             page_tokens=cache.page_tokens, step=step, plan=step.plans[self.plan_key()],
             head_scale=self.temperature, slopes=self.slopes, chunk=s.chunk)

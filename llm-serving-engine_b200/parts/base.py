@@ -124,6 +124,9 @@ class Part:
     # works from the host while the step runs: a model with such a part is never replayed as a
     # captured CUDA graph, where there is no host step and nothing may synchronise.
     needs_host_step: bool = False
+    # True for a part that keeps a running state per request which every step changes for good (a
+    # recurrence): the engine then never launches a step that it might have to drop and repeat.
+    keeps_running_state: bool = False
 
     def __init__(self, spec: Any, env: BuildEnv) -> None:
         self.spec = spec

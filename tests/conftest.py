@@ -82,3 +82,64 @@ def sharp_dirs(tmp_path_factory):
         save_file(t, str(f))
         out[name] = d
     return out
+
+
+# ---- Gubotar: small configurations that differ in every size, option and in the order of layers.
+def _ret(heads, dim, vdim, decay, rot, base, ff):
+    return {"type": "retention", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "decay": decay,
+                                            "rot": {"dims": rot, "base": base}},
+            "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+def _par(heads, kv, dim, scale, chunk, rheads, rdim, rvdim, decay, ff):
+    return {"type": "parallel",
+            "mixer": {"left": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": scale,
+                               "mask": {"size": chunk}},
+                      "right": {"heads": rheads, "dim": rdim, "vdim": rvdim, "decay": decay}},
+            "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+GUBOTAR_TINY = {
+    # retention first; partial rotation; value size unlike key size; a layer without feed-forward;
+    # grouped key heads; a chunk that is no multiple of the page
+    "G1": dict(seed=3, page_tokens=16, config={
+        "architecture": "Gubotar", "vocab": 211, "width": 96, "norm": {"eps": 1e-5},
+        "layers": [_ret(3, 16, 32, [0.9, 0.97, 0.995], 8, 10000.0, 160),
+                   _par(4, 2, 16, 0.6, 24, 2, 24, 40, [0.8, 0.99], 0),
+                   _ret(2, 48, 16, [0.999, 0.5], 48, 500.0, 64)]}),
+    # a head size that is no multiple of 16; one key head; a chunk shorter than a page; one
+    # linear-attention head; width and vocabulary that are no multiples of 8
+    "G2": dict(seed=9, page_tokens=8, config={
+        "architecture": "Gubotar", "vocab": 130, "width": 68, "norm": {"eps": 1e-6},
+        "layers": [_par(2, 1, 40, 0.35, 7, 1, 20, 64, [0.95], 96),
+                   _par(6, 6, 16, 0.5, 33, 4, 8, 8, [0.9, 0.99, 0.999, 0.3], 48)]}),
+}
+
+
+def write_gubotar(folder, name, spread=True):
+    """A random Gubotar folder. ``spread``: per-channel weights, temperatures and stored-around-zero
+    norm weights are drawn wide, so that leaving one of them out changes the logits clearly."""
+    from safetensors.torch import load_file, save_file
+
+    from llmserve_b200.config.gubotar import GubotarConfig
+    from llmserve_b200.weights import write_random_model
+
+    spec = GUBOTAR_TINY[name]
+    write_random_model(folder, GubotarConfig.from_dict(spec["config"]), spec["seed"])
+    if spread:
+        f = folder / "model.safetensors"
+        t = load_file(str(f))
+        g = torch.Generator().manual_seed(spec["seed"] + 1)
+        for k, v in t.items():
+            if v.dim() == 1 and not k.endswith("shift"):
+                around = 0.0 if (k.endswith("norm1") or k.endswith("norm2") or k == "final.norm") else 1.0
+                t[k] = (around + (torch.rand(v.shape, generator=g) - 0.5)).to(v.dtype)
+            elif k == "embed":
+                t[k] = (v.float() * 40).to(v.dtype)
+        save_file(t, str(f))
+    return folder
+
+
+@pytest.fixture(scope="session")
+def gubotar_dirs(tmp_path_factory):
+    return {name: write_gubotar(tmp_path_factory.mktemp(f"gubotar-{name}"), name) for name in GUBOTAR_TINY}

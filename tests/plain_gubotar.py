@@ -10,7 +10,6 @@ tensor names to float64 tensors.
 from __future__ import annotations
 
 import json
-import math
 from pathlib import Path
 
 import torch
@@ -68,27 +67,38 @@ def decayed_outer_product_scan(q, k, v, decay):
 
 
 # ----------------------------------------------------------------------------- mixers
+def chunked_softmax(q, k, v, scale, temp, slopes, size, start=0):
+    """q [T, H, D]; k, v [start + T, G, D] (``start`` earlier tokens are only keys). Query i
+    (absolute position start + i) sees key j <= its position of the same chunk of ``size``;
+    score = q.k * scale * temp[h] - slopes[h] * (distance)."""
+    T, H, D = q.shape
+    G = k.shape[1]
+    out = torch.zeros(T, H, v.shape[-1], dtype=F)
+    for hd in range(H):
+        g = hd // (H // G)
+        for t in range(T):
+            i = start + t
+            lo = (i // size) * size
+            js = torch.arange(lo, i + 1)
+            s = (k[lo : i + 1, g] @ q[t, hd]) * scale * temp[hd] - slopes[hd] * (i - js).to(F)
+            out[t, hd] = torch.softmax(s, 0) @ v[lo : i + 1, g]
+    return out
+
+
+def head_slopes(H):
+    return torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], dtype=F)
+
+
 def chunked_biased_attention(h, P, pre, m, eps):
     """The softmax half of the ``parallel`` mixer. h [T, W]."""
     T = h.shape[0]
     H, G, D = m["heads"], m["kv_heads"], m["dim"]
-    size = m["mask"]["size"]
     q = (h @ P[pre + "q"].T).view(T, H, D)
     k_raw = (h @ P[pre + "k"].T).view(T, G, D)
-    v = k_raw  # the values are the keys as projected
     q = rms(q, eps) * P[pre + "q.norm"]
     k = rms(k_raw, eps) * P[pre + "k.norm"]
-    out = torch.zeros(T, H, D, dtype=F)
-    for hd in range(H):
-        g = hd // (H // G)
-        slope = 2.0 ** (-8.0 * (hd + 1) / H)
-        temp = P[pre + "temp"][hd]
-        for i in range(T):
-            lo = (i // size) * size
-            js = torch.arange(lo, i + 1)
-            s = (k[lo : i + 1, g] @ q[i, hd]) * m["scale"] * temp - slope * (i - js).to(F)
-            w = torch.softmax(s, 0)
-            out[i, hd] = w @ v[lo : i + 1, g]
+    # the values are the keys as projected
+    out = chunked_softmax(q, k, k_raw, m["scale"], P[pre + "temp"], head_slopes(H), m["mask"]["size"])
     return out.reshape(T, H * D) @ P[pre + "o"].T
 
 
@@ -158,5 +168,10 @@ def model_logits(folder, tokens):
     return forward(cfg, P, tokens).float()
 
 
-def _unused():  # keeps math imported for callers that patch constants
-    return math.pi
+def greedy(folder, prompt, n):
+    """n tokens generated greedily after ``prompt`` (the whole sequence is run again each time)."""
+    cfg, P = load(folder)
+    tokens = list(prompt)
+    for _ in range(n):
+        tokens.append(int(forward(cfg, P, tokens)[-1].argmax()))
+    return tokens[len(prompt):]

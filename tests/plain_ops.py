@@ -164,15 +164,16 @@ class PlainOps:
 
     def norm_rope_kv_write(self, qkv, *, num_heads, num_kv_heads, head_dim, values_are_keys, q_weight,
                            k_weight, eps, positions, token_seq, cos, sin, k_pages, v_pages,
-                           block_tables, page_tokens, out_dtype):
+                           block_tables, page_tokens, out_dtype, norm_dim=None):
         T, D = qkv.shape[0], head_dim
+        nd = norm_dim or head_dim
         nv = 0 if values_are_keys else num_kv_heads
         heads = qkv.float().view(T, num_heads + num_kv_heads + nv, D)
         q, k = heads[:, :num_heads], heads[:, num_heads : num_heads + num_kv_heads]
         v = k if values_are_keys else heads[:, num_heads + num_kv_heads :]
         if q_weight is not None:
-            q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight
-            k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_weight
+            q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) / nd + eps) * q_weight
+            k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) / nd + eps) * k_weight
         pos = positions.long()
         if cos is not None:
             c, s_ = cos[pos][:, None, :], sin[pos][:, None, :]
