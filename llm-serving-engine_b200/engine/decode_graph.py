@@ -236,6 +236,7 @@ class DecodeGraphs:
         self.mixed_plannable = all(hasattr(m, "plan_rows") for m, _ in runner.planners.values())
         # a part that works from the host while a step runs rules out captures altogether
         self.capturable = not any(getattr(p, "needs_host_step", False) for p in model.parts())
+        self.keeps_running_state = any(getattr(p, "keeps_running_state", False) for p in model.parts())
 
     def padded(self, n: int) -> int:
         """The captured batch size that serves ``n`` rows."""
@@ -512,8 +513,11 @@ class DecodeGraphs:
         return runner.ops.sample(logits, *g.sample_args, kinds=g.kinds) if g.sampled else logits
 
     def _capture(self, g) -> None:
-        """Run the step once uncaptured (lazy allocations happen here; its writes are idempotent),
-        then record it. The record is made with ``capture_begin`` / ``capture_end`` rather than the
+        """Run the step once uncaptured (lazy allocations happen here), then record it. The
+        uncaptured run's writes into pages are the ones the replay makes again. Running states are
+        another matter: a part that advances a state per request would advance it twice, so for
+        such models the uncaptured run has every row on the spare state slot, and the rows' own
+        slots are put back before the record. The record is made with ``capture_begin`` / ``capture_end`` rather than the
         ``torch.cuda.graph`` context, which collects garbage and empties the allocator's cache
         first: with captures made while requests are served that costs more than the capture."""
         ops = self.runner.ops
@@ -523,7 +527,14 @@ class DecodeGraphs:
         side = self.side
         side.wait_stream(cur)
         with torch.cuda.stream(side):
-            self._forward(g)
+            if self.keeps_running_state:
+                slots = g.step.state_slots
+                slots.fill_(self.runner.pools.spare_slot)
+                self._forward(g)
+                o = g.off["state_slots"]
+                slots.copy_(g.host[o : o + slots.numel()], non_blocking=True)
+            else:
+                self._forward(g)
         cur.wait_stream(side)
         torch.cuda.synchronize()
         before = ops.launches
