@@ -1,7 +1,7 @@
 """Throughput of the engine on one B200, random weights, synthetic token ids.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--parity]
-    python bench.py --workload continuous | long
+    python bench.py --workload continuous | long | designs
     python bench.py --impl reference [--steps K] [--warmup W]
 
 The default workload is decoding at SmolLM2-1.7B sizes: a "step" is one decode step of the whole
@@ -18,6 +18,11 @@ implementation in ``tests/``. One JSON line is printed.
 and a float32 replay of one 8192-token sequence against the plain implementation) follow the
 reference's own harness (src/llmserve/bench/run.py:96,124-176): fixed output lengths, greedy, a
 warm-up run that is thrown away, one JSON line with the environment.
+
+``--workload designs`` puts four Gubotar layers (parallel, retention, retention, parallel) beside
+four Llama layers of the same width, feed-forward and head sizes, at SmolLM2-360M and -1.7B layer
+sizes: a 2048-token prompt in one step, with its device time by kernel, and decode steps at batch
+1, 8 and 64 behind 2048-token prompts.
 
 ``--impl reference`` runs the unmodified reference package from ``baseline/_ref`` through its own
 ``LLMEngine`` on the same device, sizes and workload, and prints the same line.
@@ -563,6 +568,101 @@ def long_parity(layers: int) -> dict:
 
 
 # --------------------------------------------------------------------------- the reference
+# --------------------------------------------------------------------------- two designs side by side
+def gubotar_layers(width, heads, kv_heads, head_dim, ff, chunk=512, state_dim=128):
+    """Four Gubotar layers (parallel, retention, retention, parallel) at a Llama layer's sizes:
+    the softmax half has the Llama layer's heads; the linear-attention heads are ``state_dim`` wide."""
+    lin = max(1, width // state_dim)
+    decay = [1 - 2.0 ** (-5 - 5 * h / max(1, lin - 1)) for h in range(lin)]
+    mlp = {"kind": "dense", "ff": ff}
+    par = {"type": "parallel", "mlp": mlp, "mixer": {
+        "left": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim,
+                 "scale": head_dim ** -0.5, "mask": {"size": chunk}},
+        "right": {"heads": lin, "dim": state_dim, "vdim": state_dim, "decay": decay}}}
+    ret = {"type": "retention", "mlp": mlp, "mixer": {
+        "heads": lin, "dim": state_dim, "vdim": state_dim, "decay": decay,
+        "rot": {"dims": state_dim, "base": 10000.0}}}
+    return [par, ret, ret, par]
+
+
+def kernel_profile(fn, reps=3) -> dict:
+    """Device time of ``fn()`` by kernel, from the framework's profiler: microseconds per call."""
+    import collections
+
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    fn()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(reps):
+            fn()
+        torch.cuda.synchronize()
+    fam = collections.Counter()
+    for e in prof.events():
+        if e.device_type == torch.autograd.DeviceType.CUDA:
+            key = e.name.split("(")[0].split("<")[0].replace("void ", "").replace("lse::", "")
+            fam[key] += (e.time_range.end - e.time_range.start) / reps
+    return {k: round(v, 1) for k, v in fam.most_common(12)}
+
+
+def designs_main(args) -> int:
+    """``--workload designs``: prefill and decode of four Gubotar layers beside four Llama layers of
+    the same width, feed-forward and head sizes (random weights, bfloat16), through the engine."""
+    import torch
+
+    from llmserve_b200 import EngineConfig, LLMEngine, SamplingParams
+    from llmserve_b200.models.hub import preset_config_dict
+
+    pk = peaks()
+    out = []
+    for alias in ("smollm2-360m", "smollm2-1.7b"):
+        ll = preset_config_dict(alias)
+        w, heads, kv, hd, ff = (ll["hidden_size"], ll["num_attention_heads"], ll["num_key_value_heads"],
+                                ll["head_dim"], ll["intermediate_size"])
+        arms = {
+            "llama": (f"random:{alias}", {"num_hidden_layers": 4}),
+            "gubotar": ("random:gubotar-2048", {"width": w, "vocab": ll["vocab_size"],
+                                                 "layers": gubotar_layers(w, heads, kv, hd, ff, state_dim=hd if w < 2048 else 128)}),
+        }
+        row = {"sizes": f"{alias}: width {w}, ff {ff}, {heads} heads of {hd}, 4 layers"}
+        for name, (model, over) in arms.items():
+            page = args.page_tokens
+            per_req = -(-(PROMPT_LEN + 2 * (args.steps + args.warmup) + 64) // page) * page
+            engine = LLMEngine(EngineConfig(
+                model=model, dtype="bfloat16", seed=4, block_size=page, num_kv_blocks=64 * per_req // page,
+                max_model_len=CONTEXT, max_num_seqs=64, max_num_batched_tokens=PREFILL_TOKENS,
+                config_overrides=over))
+            r = {}
+            ms = measure_prefill(engine)
+            r["prefill_2048_ms"] = round(ms, 3)
+            r["prefill_tok_s"] = round(PREFILL_TOKENS * 1e3 / ms)
+            sp = SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True)
+            prompt = random_prompts(1, PREFILL_TOKENS, ll["vocab_size"], 5)[0]
+
+            def one_prefill():
+                rid = engine.add_request(prompt, sp)
+                engine.step()
+                engine.abort_request(rid)
+
+            r["prefill_kernels_us"] = kernel_profile(one_prefill)
+            for b in (1, 8, 64):
+                d = measure_decode(engine, b, args.steps, args.warmup, seed=20 + b)
+                r[f"decode_b{b}_ms"] = round(d["dev_ms"], 4)
+                r[f"decode_b{b}_tok_s"] = round(b * 1e3 / d["dev_ms"])
+                r[f"decode_b{b}_launches"] = d["launches"]
+            if args.timeline:
+                r["decode_b8_timeline"] = step_timeline(engine, 8, seed=3)
+            row[name] = r
+            del engine
+            torch.cuda.empty_cache()
+        out.append(row)
+    print(json.dumps({"workload": "designs", "dtype": "bf16", "prompt_len": PROMPT_LEN,
+                      "data": "synthetic: uniform random token ids, random-init weights (seed 4)",
+                      "steps": args.steps, "warmup": max(3, args.warmup), "peaks": pk, "designs": out}))
+    return 0
+
+
 def unavailable(why: str) -> int:
     print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
@@ -671,7 +771,7 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "continuous", "long"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "continuous", "long", "designs"])
     ap.add_argument("--model", default="smollm2-1.7b")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0 = all)")
@@ -695,7 +795,8 @@ def main() -> int:
     if args.impl == "reference":
         return reference_main(args)
     sys.path.insert(0, str(ROOT))
-    return {"decode": decode_main, "continuous": continuous_main, "long": long_main}[args.workload](args)
+    return {"decode": decode_main, "continuous": continuous_main, "long": long_main,
+            "designs": designs_main}[args.workload](args)
 
 
 if __name__ == "__main__":

@@ -539,7 +539,8 @@ void norm_rope_kv_write(const Tensor& qkv, Tensor& q_out, int64_t nq, int64_t nk
 
 void decay_linear_attention(const Tensor& proj, Tensor& out, Tensor& state, const Tensor& decay, const Tensor& cu_q,
                             const Tensor& ctx_lens, const Tensor& slots, int64_t H, int64_t dk, int64_t dv,
-                            const OptTensor& cos, const OptTensor& sin, bool silu, double key_scale) {
+                            const OptTensor& cos, const OptTensor& sin, bool silu, double key_scale,
+                            int64_t max_chunks, const OptTensor& chunks) {
   check_f32(proj, "proj");
   check_f32(out, "out");
   check_f32(state, "state");
@@ -564,11 +565,21 @@ void decay_linear_attention(const Tensor& proj, Tensor& out, Tensor& state, cons
                 "decay_linear_attention: cos and sin must be [positions, rotated dims / 2]");
     rot = 2 * (int)cos->size(1);
   }
+  float* chunk_ptr = nullptr;
+  if (max_chunks > 1) {
+    TORCH_CHECK(chunks.has_value(), "decay_linear_attention: chunked portions need the scratch");
+    check_f32(*chunks, "chunks");
+    // every sequence of more than one chunk holds at most tokens / chunk + 1 of them
+    const int64_t L = lse_linear_attention_chunk();
+    const int64_t most = proj.size(0) / L + ctx_lens.numel();
+    TORCH_CHECK(chunks->numel() >= most * H * dv * dk, "decay_linear_attention: the scratch is too small");
+    chunk_ptr = chunks->data_ptr<float>();
+  }
   done(lse_decay_linear_attention(proj.data_ptr<float>(), proj.size(1), out.data_ptr<float>(), state.data_ptr<float>(),
                                   decay.data_ptr<float>(), cu_q.data_ptr<int>(), ctx_lens.data_ptr<int>(),
                                   slots.data_ptr<int>(), (int)ctx_lens.numel(), (int)H, (int)dk, (int)dv,
                                   cos ? cos->data_ptr<float>() : nullptr, sin ? sin->data_ptr<float>() : nullptr, rot,
-                                  silu ? 1 : 0, (float)key_scale, stream()),
+                                  silu ? 1 : 0, (float)key_scale, (int)max_chunks, chunk_ptr, stream()),
        "decay_linear_attention");
 }
 
@@ -781,6 +792,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gated_group_norm", &gated_group_norm);
   m.def("norm_rope_kv_write", &norm_rope_kv_write);
   m.def("decay_linear_attention", &decay_linear_attention);
+  m.def("linear_attention_chunk", []() { return (int64_t)lse_linear_attention_chunk(); });
   m.def("paged_attention_from_sums", &paged_attention_from_sums);
   m.def("attention_takes_sums", &attention_takes_sums);
   m.def("sample", &sample, py::arg("logits"), py::arg("temperature"), py::arg("top_k"), py::arg("top_p"),

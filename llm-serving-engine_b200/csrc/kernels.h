@@ -152,10 +152,14 @@ int lse_norm_rope_kv_write(const float* qkv, void* q_out, int dtype, int T, int 
 // proj [T, stride]: per row q (H*dk) | k (H*dk) | v (H*dv) | anything else. silu != 0: silu on q,
 // k and v. The first `rot` dims of q and k are rotated (pairs (i, i + rot/2), cos/sin
 // [positions, rot/2]); k is then multiplied by key_scale. state [slots, H, dv, dk] float32.
-// dk <= 256.
+// dk <= 256. A portion of more than lse_linear_attention_chunk() tokens runs as chunks side by
+// side (three launches); max_chunks is the largest number of chunks of any sequence of the step
+// (or a bound on it), and chunks a scratch of (sum over sequences with more than one chunk of
+// their chunks) * H * dv * dk floats, needed when max_chunks > 1.
+int lse_linear_attention_chunk(void);
 int lse_decay_linear_attention(const float* proj, long long stride, float* out, float* state,
                                const float* decay, const int* cu_q, const int* ctx_lens,
                                const int* slots, int num_seqs, int H, int dk, int dv,
                                const float* cos, const float* sin, int rot, int silu,
-                               float key_scale, cudaStream_t stream);
+                               float key_scale, int max_chunks, float* chunks, cudaStream_t stream);
 }

@@ -255,14 +255,23 @@ __global__ void norm_rope_kv_write_kernel(const float* __restrict__ qkv, T* __re
 }
 
 // ------------------------------------------------------------------------------------ linear attention with decay
-// S_t = decay * S_{t-1} + k_t v_t^T,  o_t = S_t^T q_t, stepped token by token in float32.
-// One block per (head, slice of CB value columns, sequence); 256 threads. A column of S (key_dim
-// values) is shared by P neighbouring lanes, RPT = 16 rows each, held in registers across the
-// whole portion; the P partial dot products of o are added with shuffles. Columns are
-// independent of one another, so slices of a head's columns run as separate blocks. q, k (after
-// activation, rotation and scaling) and v of TT tokens are staged in shared memory per pass.
-// The state is stored transposed, [slot][head][value_dim][key_dim]: a thread's rows are
-// contiguous there.
+// S_t = decay * S_{t-1} + k_t v_t^T,  o_t = S_t^T q_t, in float32 on the CUDA cores.
+// One block per (head, slice of CB value columns, chunk of the portion, sequence); 256 threads.
+// A column of S (key_dim values) is shared by P neighbouring lanes, RPT = 16 rows each, held in
+// registers while the block steps through its tokens; the P partial dot products of o are added
+// with shuffles. Columns are independent of one another, so slices of a head's columns run as
+// separate blocks. q, k (after activation, rotation and scaling) and v of TT tokens are staged in
+// shared memory per pass. The state is stored transposed, [slot][head][value_dim][key_dim]: a
+// thread's rows are contiguous there.
+//
+// A portion longer than L tokens is cut into chunks of L that run side by side, in three launches:
+//   A  every chunk steps through its tokens from a zero state (the first chunk from the request's
+//      state) and leaves its outputs and its final state (chunk c: E_c) in a scratch;
+//   B  the chunks' states are chained, element by element: F_0 = E_0, F_c = decay^len_c F_{c-1} + E_c;
+//      the last one is the request's new state;
+//   C  chunk c >= 1 adds what the state before it contributes: o_t += decay^(t - t_c + 1) F_{c-1}^T q_t.
+// A portion of at most L tokens (a single token, above all) is one chunk: launch A alone, which
+// then reads and writes the request's state itself.
 constexpr int LA_RPT = 16, LA_TT = 16, LA_THREADS = 256, LA_PAD = 4;
 
 struct LinAttnArgs {
@@ -270,6 +279,7 @@ struct LinAttnArgs {
   long long stride;
   float* out;             // [T, H * dv]
   float* state;           // [slots, H, dv, dk]
+  float* chunks;          // scratch [chunks of all chunked sequences, H, dv, dk], or null
   const float* decay;     // [H]
   const int* cu_q;
   const int* ctx_lens;
@@ -279,17 +289,37 @@ struct LinAttnArgs {
   int H, dk, dv, rot, silu;
   float key_scale;
   int P, CB;              // lanes per column; columns per block
+  int L;                  // chunk length
+  int phase;              // 0: launch A, 2: launch C
 };
+
+// Index of a sequence's first chunk in the scratch: only sequences of more than one chunk have any.
+__device__ __forceinline__ int chunk_base(const int* cu_q, int seq, int L) {
+  int base = 0;
+  for (int s = 0; s < seq; ++s) {
+    const int nc = (cu_q[s + 1] - cu_q[s] + L - 1) / L;
+    base += nc > 1 ? nc : 0;
+  }
+  return base;
+}
 
 __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(const LinAttnArgs a) {
   extern __shared__ float la_smem[];
   pdl_trigger();
-  const int P = a.P, CB = a.CB, dk = a.dk, dv = a.dv, H = a.H;
+  const int P = a.P, CB = a.CB, dk = a.dk, dv = a.dv, H = a.H, L = a.L;
   const int slices = (dv + CB - 1) / CB;
   const int h = blockIdx.x / slices, cb = blockIdx.x - h * slices;
-  const int seq = blockIdx.y;
+  const int seq = blockIdx.z;
   const int r0 = a.cu_q[seq], n = a.cu_q[seq + 1] - r0;
+  const int num_chunks = (n + L - 1) / L;
+  const bool add_pass = a.phase == 2;
+  const int c = blockIdx.y + (add_pass ? 1 : 0);
+  if (c >= num_chunks) {
+    pdl_wait();  // no block leaves before the kernels before this one are done: the next kernel counts on it
+    return;
+  }
   const int pos0 = a.ctx_lens[seq] - n;
+  const int t_begin = c * L, t_end = min(n, t_begin + L);
   const int p = threadIdx.x % P, jl = threadIdx.x / P;
   const int j = cb * CB + jl;
   const int ldq = P * (LA_RPT + LA_PAD);
@@ -298,14 +328,22 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
   float* vs = ks + LA_TT * ldq;         // [TT][CB]
   const float decay = a.decay[h];
   float S[LA_RPT];
-  float* st = a.state + (((size_t)a.slots[seq] * H + h) * dv + (j < dv ? j : 0)) * dk + p * LA_RPT;
+  const size_t column = ((size_t)h * dv + (j < dv ? j : 0)) * dk + p * LA_RPT;
+  const size_t per_state = (size_t)H * dv * dk;
+  float* st = a.state + (size_t)a.slots[seq] * per_state + column;
+  float* chunk_states = nullptr;
+  if (num_chunks > 1) chunk_states = a.chunks + (size_t)chunk_base(a.cu_q, seq, L) * per_state + column;
   pdl_wait();
+  {
+    const float* from = add_pass ? chunk_states + (size_t)(c - 1) * per_state : st;
+    const bool read = add_pass || (c == 0 && pos0 > 0);
 #pragma unroll
-  for (int r = 0; r < LA_RPT; ++r)
-    S[r] = (pos0 > 0 && j < dv && p * LA_RPT + r < dk) ? st[r] : 0.f;
+    for (int r = 0; r < LA_RPT; ++r) S[r] = (read && j < dv && p * LA_RPT + r < dk) ? from[r] : 0.f;
+  }
   const int half = a.rot / 2;
-  for (int t0 = 0; t0 < n; t0 += LA_TT) {
-    const int tn = min(LA_TT, n - t0);
+  float carried = 1.f;  // launch C: decay^(tokens of the chunk so far)
+  for (int t0 = t_begin; t0 < t_end; t0 += LA_TT) {
+    const int tn = min(LA_TT, t_end - t0);
     __syncthreads();
     for (int idx = threadIdx.x; idx < tn * P * LA_RPT; idx += LA_THREADS) {
       const int tt = idx / (P * LA_RPT), i = idx - tt * (P * LA_RPT);
@@ -314,7 +352,7 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
         const float* row = a.proj + (size_t)(r0 + t0 + tt) * a.stride + (size_t)h * dk;
         const float* krow = row + (size_t)H * dk;
         q = row[i];
-        k = krow[i];
+        k = add_pass ? 0.f : krow[i];
         if (a.silu) {
           q = silu_f(q);
           k = silu_f(k);
@@ -322,15 +360,15 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
         if (i < a.rot) {
           const int f = i < half ? i : i - half;
           const size_t at = (size_t)(pos0 + t0 + tt) * half + f;
-          const float c = a.cos[at], s = a.sin[at];
+          const float cs = a.cos[at], sn = a.sin[at];
           const int ip = i < half ? i + half : i - half;
-          float qp = row[ip], kp = krow[ip];
+          float qp = row[ip], kp = add_pass ? 0.f : krow[ip];
           if (a.silu) {
             qp = silu_f(qp);
             kp = silu_f(kp);
           }
-          q = i < half ? q * c - qp * s : q * c + qp * s;
-          k = i < half ? k * c - kp * s : k * c + kp * s;
+          q = i < half ? q * cs - qp * sn : q * cs + qp * sn;
+          k = i < half ? k * cs - kp * sn : k * cs + kp * sn;
         }
         k *= a.key_scale;
       }
@@ -338,41 +376,85 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
       qs[at] = q;
       ks[at] = k;
     }
-    for (int idx = threadIdx.x; idx < tn * CB; idx += LA_THREADS) {
-      const int tt = idx / CB, c = idx - tt * CB;
-      float v = 0.f;
-      if (cb * CB + c < dv) {
-        v = a.proj[(size_t)(r0 + t0 + tt) * a.stride + (size_t)2 * H * dk + (size_t)h * dv + cb * CB + c];
-        if (a.silu) v = silu_f(v);
+    if (!add_pass)
+      for (int idx = threadIdx.x; idx < tn * CB; idx += LA_THREADS) {
+        const int tt = idx / CB, cc = idx - tt * CB;
+        float v = 0.f;
+        if (cb * CB + cc < dv) {
+          v = a.proj[(size_t)(r0 + t0 + tt) * a.stride + (size_t)2 * H * dk + (size_t)h * dv + cb * CB + cc];
+          if (a.silu) v = silu_f(v);
+        }
+        vs[idx] = v;
       }
-      vs[idx] = v;
-    }
     __syncthreads();
     for (int tt = 0; tt < tn; ++tt) {
-      const float vj = vs[tt * CB + jl];
       const float4* q4 = reinterpret_cast<const float4*>(qs + tt * ldq + p * (LA_RPT + LA_PAD));
-      const float4* k4 = reinterpret_cast<const float4*>(ks + tt * ldq + p * (LA_RPT + LA_PAD));
       float acc = 0.f;
+      if (!add_pass) {
+        const float vj = vs[tt * CB + jl];
+        const float4* k4 = reinterpret_cast<const float4*>(ks + tt * ldq + p * (LA_RPT + LA_PAD));
 #pragma unroll
-      for (int r4 = 0; r4 < LA_RPT / 4; ++r4) {
-        const float4 q = q4[r4], k = k4[r4];
-        S[4 * r4 + 0] = fmaf(decay, S[4 * r4 + 0], k.x * vj);
-        S[4 * r4 + 1] = fmaf(decay, S[4 * r4 + 1], k.y * vj);
-        S[4 * r4 + 2] = fmaf(decay, S[4 * r4 + 2], k.z * vj);
-        S[4 * r4 + 3] = fmaf(decay, S[4 * r4 + 3], k.w * vj);
-        acc = fmaf(S[4 * r4 + 0], q.x, acc);
-        acc = fmaf(S[4 * r4 + 1], q.y, acc);
-        acc = fmaf(S[4 * r4 + 2], q.z, acc);
-        acc = fmaf(S[4 * r4 + 3], q.w, acc);
+        for (int r4 = 0; r4 < LA_RPT / 4; ++r4) {
+          const float4 q = q4[r4], k = k4[r4];
+          S[4 * r4 + 0] = fmaf(decay, S[4 * r4 + 0], k.x * vj);
+          S[4 * r4 + 1] = fmaf(decay, S[4 * r4 + 1], k.y * vj);
+          S[4 * r4 + 2] = fmaf(decay, S[4 * r4 + 2], k.z * vj);
+          S[4 * r4 + 3] = fmaf(decay, S[4 * r4 + 3], k.w * vj);
+          acc = fmaf(S[4 * r4 + 0], q.x, acc);
+          acc = fmaf(S[4 * r4 + 1], q.y, acc);
+          acc = fmaf(S[4 * r4 + 2], q.z, acc);
+          acc = fmaf(S[4 * r4 + 3], q.w, acc);
+        }
+      } else {
+#pragma unroll
+        for (int r4 = 0; r4 < LA_RPT / 4; ++r4) {
+          const float4 q = q4[r4];
+          acc = fmaf(S[4 * r4 + 0], q.x, acc);
+          acc = fmaf(S[4 * r4 + 1], q.y, acc);
+          acc = fmaf(S[4 * r4 + 2], q.z, acc);
+          acc = fmaf(S[4 * r4 + 3], q.w, acc);
+        }
+        carried *= decay;
       }
       for (int o = P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (p == 0 && j < dv) a.out[(size_t)(r0 + t0 + tt) * ((size_t)H * dv) + (size_t)h * dv + j] = acc;
+      if (p == 0 && j < dv) {
+        float* dst = a.out + (size_t)(r0 + t0 + tt) * ((size_t)H * dv) + (size_t)h * dv + j;
+        *dst = add_pass ? *dst + carried * acc : acc;
+      }
     }
   }
-  if (j < dv)
+  if (add_pass || j >= dv) return;
+  float* to = num_chunks > 1 ? chunk_states + (size_t)c * per_state : st;
 #pragma unroll
-    for (int r = 0; r < LA_RPT; ++r)
-      if (p * LA_RPT + r < dk) st[r] = S[r];
+  for (int r = 0; r < LA_RPT; ++r)
+    if (p * LA_RPT + r < dk) to[r] = S[r];
+}
+
+// Launch B: one thread per element of the state and sequence of more than one chunk.
+__global__ void chain_chunk_states_kernel(float* __restrict__ chunks, float* __restrict__ state,
+                                          const float* __restrict__ decay, const int* __restrict__ cu_q,
+                                          const int* __restrict__ slots, int H, int dv, int dk, int L) {
+  pdl_trigger();
+  const int seq = blockIdx.y;
+  const int n = cu_q[seq + 1] - cu_q[seq];
+  const int num_chunks = (n + L - 1) / L;
+  const size_t per_state = (size_t)H * dv * dk;
+  const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (num_chunks <= 1 || e >= per_state) {
+    pdl_wait();  // as above
+    return;
+  }
+  float* mine = chunks + (size_t)chunk_base(cu_q, seq, L) * per_state + e;
+  const float d = decay[e / ((size_t)dv * dk)];
+  const float whole = powf(d, (float)L);
+  pdl_wait();
+  float S = mine[0];
+  for (int c = 1; c < num_chunks; ++c) {
+    const int len = min(L, n - c * L);
+    S = fmaf(len == L ? whole : powf(d, (float)len), S, mine[(size_t)c * per_state]);
+    mine[(size_t)c * per_state] = S;
+  }
+  state[(size_t)slots[seq] * per_state + e] = S;
 }
 
 static int pow2_at_least(int n) {
@@ -476,24 +558,35 @@ extern "C" int lse_norm_rope_kv_write(const float* qkv, void* q_out, int dtype, 
   return LSE_CHECK_LAUNCH();
 }
 
+extern "C" int lse_linear_attention_chunk(void) { return 64; }
+
 extern "C" int lse_decay_linear_attention(const float* proj, long long stride, float* out, float* state,
                                           const float* decay, const int* cu_q, const int* ctx_lens,
                                           const int* slots, int num_seqs, int H, int dk, int dv,
                                           const float* cos, const float* sin, int rot, int silu,
-                                          float key_scale, cudaStream_t stream) {
+                                          float key_scale, int max_chunks, float* chunks,
+                                          cudaStream_t stream) {
   if (num_seqs <= 0) return LSE_OK;
   if (H <= 0 || dk <= 0 || dv <= 0 || dk > 256 || rot < 0 || rot > dk || rot % 2 || (rot && (!cos || !sin)) ||
-      num_seqs > 65535)
+      num_seqs > 65535 || max_chunks < 1 || max_chunks > 65535 || (max_chunks > 1 && !chunks))
     return LSE_BAD_ARGUMENT;
   LinAttnArgs a;
-  a.proj = proj; a.stride = stride; a.out = out; a.state = state; a.decay = decay; a.cu_q = cu_q;
-  a.ctx_lens = ctx_lens; a.slots = slots; a.cos = cos; a.sin = sin; a.H = H; a.dk = dk; a.dv = dv;
-  a.rot = rot; a.silu = silu; a.key_scale = key_scale;
+  a.proj = proj; a.stride = stride; a.out = out; a.state = state; a.chunks = chunks; a.decay = decay;
+  a.cu_q = cu_q; a.ctx_lens = ctx_lens; a.slots = slots; a.cos = cos; a.sin = sin; a.H = H; a.dk = dk;
+  a.dv = dv; a.rot = rot; a.silu = silu; a.key_scale = key_scale;
   a.P = pow2_at_least((dk + LA_RPT - 1) / LA_RPT);
   a.CB = LA_THREADS / a.P;
+  a.L = lse_linear_attention_chunk();
+  a.phase = 0;
   const int slices = (dv + a.CB - 1) / a.CB;
   const size_t smem = ((size_t)2 * LA_TT * a.P * (LA_RPT + LA_PAD) + (size_t)LA_TT * a.CB) * sizeof(float);
-  dim3 grid(H * slices, num_seqs);
-  launch(decay_linear_attention_kernel, grid, LA_THREADS, smem, stream, a);
+  launch(decay_linear_attention_kernel, dim3(H * slices, max_chunks, num_seqs), LA_THREADS, smem, stream, a);
+  if (max_chunks > 1) {
+    const size_t per_state = (size_t)H * dv * dk;
+    launch(chain_chunk_states_kernel, dim3((unsigned)((per_state + 255) / 256), num_seqs), 256, 0, stream,
+           chunks, state, decay, cu_q, slots, H, dv, dk, a.L);
+    a.phase = 2;
+    launch(decay_linear_attention_kernel, dim3(H * slices, max_chunks - 1, num_seqs), LA_THREADS, smem, stream, a);
+  }
   return LSE_CHECK_LAUNCH();
 }

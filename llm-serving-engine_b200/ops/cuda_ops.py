@@ -458,11 +458,29 @@ class CudaOps:
 
     def decay_linear_attention(self, proj, *, num_heads, key_dim, value_dim, decay, state, step,
                                activation, key_scale, cos, sin):
-        out = torch.empty(proj.shape[0], num_heads * value_dim, dtype=torch.float32, device=proj.device)
+        """Portions longer than the kernel's chunk run as chunks side by side (three launches and
+        a scratch for the chunks' states); steps of single tokens and short portions are one launch."""
+        T = proj.shape[0]
+        out = torch.empty(T, num_heads * value_dim, dtype=torch.float32, device=proj.device)
+        L = self._la_chunk = getattr(self, "_la_chunk", None) or int(self.ext.linear_attention_chunk())
+        host = getattr(step, "host", None)
+        longest = int(host.q_lens.max()) if host is not None else T - (int(step.cu_q.shape[0]) - 2)
+        max_chunks = max(1, -(-longest // L))
+        scratch = None
+        if max_chunks > 1:
+            need = (T // L + int(step.cu_q.shape[0]) - 1) * num_heads * value_dim * key_dim
+            scratch = getattr(self, "_la_scratch", None)
+            if scratch is None or scratch.numel() < need:
+                if torch.cuda.is_current_stream_capturing():
+                    raise RuntimeError("the linear-attention scratch must exist before graph capture")
+                # a captured step keeps the address of the scratch it was recorded with: an
+                # outgrown scratch is kept alive beside its successor
+                self._la_outgrown = getattr(self, "_la_outgrown", []) + ([scratch] if scratch is not None else [])
+                scratch = self._la_scratch = torch.empty(need, dtype=torch.float32, device=proj.device)
         self.ext.decay_linear_attention(proj, out, state, decay, step.cu_q, step.ctx_lens, step.state_slots,
                                         num_heads, key_dim, value_dim, cos, sin, activation == "silu",
-                                        float(key_scale))
-        self.launches += 1
+                                        float(key_scale), max_chunks, scratch)
+        self.launches += 3 if max_chunks > 1 else 1
         return out
 
     def gated_group_norm(self, o, proj, *, gate_offset, group, weight, eps, gate_activation, out_dtype):

@@ -87,29 +87,61 @@ def rotary_tables(rot, base, n):
                                               (2, 64, 64, 32, True), (1, 128, 96, 0, False), (2, 256, 8, 0, True),
                                               (1, 33, 300, 0, False)])
 def test_decay_linear_attention(ops, H, dk, dv, rot, silu):
-    """A whole prompt against the plain recurrence; the same prompt in portions beside another
-    request, through state slots, gives the same bits as the whole prompt."""
-    T, extra = 75, 11  # extra columns after q|k|v stand for the gate
+    """A whole prompt (more than one chunk of the kernel) against the plain recurrence; the same
+    prompt in short portions beside another request, through state slots; and token by token,
+    which gives the bits of the short portions."""
+    T, extra = 150, 11  # extra columns after q|k|v stand for the gate
     decay = [0.999, 0.9, 0.5][:H]
     proj = rnd(T, 2 * H * dk + H * dv + extra, seed=H + dk, scale=0.7)
-    cos, sin = rotary_tables(rot, 1e4, 128) if rot else (None, None)
+    cos, sin = rotary_tables(rot, 1e4, 256) if rot else (None, None)
     kw = dict(num_heads=H, key_dim=dk, value_dim=dv, decay=torch.tensor(decay).cuda(),
               activation="silu" if silu else "none", key_scale=dk ** -0.5, cos=cos, sin=sin)
+    ref = linear_attention_reference(proj, H, dk, dv, decay, silu, rot, 1e4, dk ** -0.5)
     state = torch.full((4, H, dv, dk), 1e4).cuda()  # stale contents that must never be read at position 0
     whole = ops.decay_linear_attention(proj.cuda(), state=state, step=batch([T], [0], [1]), **kw)
-    close(whole, linear_attention_reference(proj, H, dk, dv, decay, silu, rot, 1e4, dk ** -0.5), 2e-5, "whole")
+    close(whole, ref, 2e-5, "whole")
     # portions of the same request on slot 2, another request's rows on slot 0 in between
-    other = rnd(40, proj.shape[1], seed=99)
+    other = rnd(140, proj.shape[1], seed=99)
     state2 = torch.full((4, H, dv, dk), -1e4).cuda()
     got, at, oat = [], 0, 0
-    for n, m in [(33, 2), (2, 0), (1, 1), (1, 20), (38, 1)]:
+    for n, m in [(33, 2), (2, 0), (1, 1), (1, 20), (64, 1), (49, 100)]:
         rows = [proj[at : at + n]] + ([other[oat : oat + m]] if m else [])
         step = batch([n] + ([m] if m else []), [at] + ([oat] if m else []), [2] + ([0] if m else []))
         out = ops.decay_linear_attention(torch.cat(rows).cuda(), state=state2, step=step, **kw)
         got.append(out[:n])
         at, oat = at + n, oat + m
-    assert torch.equal(torch.cat(got), whole)
-    assert torch.equal(state2[2], state[1]) and bool((state2[3] == -1e4).all())
+    got = torch.cat(got)
+    close(got, ref, 2e-5, "portions")
+    close(state2[2], state[1].cpu(), 2e-5, "final state")
+    assert bool((state2[3] == -1e4).all())
+    state3 = torch.zeros(4, H, dv, dk).cuda()
+    single = torch.cat([ops.decay_linear_attention(proj[t : t + 1].cuda(), state=state3, step=batch([1], [t], [3]), **kw)
+                        for t in range(T)])
+    assert torch.equal(single, got) and torch.equal(state3[3], state2[2])
+
+
+def test_linear_attention_chunked_and_short_sequences_in_one_step(ops):
+    """Three long portions (several chunks each, one continuing from a state) beside single tokens."""
+    H, dk, dv = 2, 128, 128
+    decay = [0.99, 0.9995]
+    width = 2 * H * dk + H * dv
+    kw = dict(num_heads=H, key_dim=dk, value_dim=dv, decay=torch.tensor(decay).cuda(), activation="none",
+              key_scale=dk ** -0.5, cos=None, sin=None)
+    seqs = [rnd(n, width, seed=10 + i, scale=0.5) for i, n in enumerate([300, 1, 129, 1, 450])]
+    state = torch.full((6, H, dv, dk), 3e3).cuda()
+    # the first 40 rows of sequence 4 and 7 rows of sequence 1 and 3 ran in an earlier step
+    first = ops.decay_linear_attention(torch.cat([seqs[4][:40], rnd(7, width, seed=30), rnd(7, width, seed=31)]).cuda(),
+                                       state=state, step=batch([40, 7, 7], [0, 0, 0], [4, 1, 3]), **kw)
+    rows = torch.cat([seqs[0], seqs[1], seqs[2], seqs[3], seqs[4][40:]])
+    out = ops.decay_linear_attention(rows.cuda(), state=state,
+                                     step=batch([300, 1, 129, 1, 410], [0, 7, 0, 7, 40], [0, 1, 2, 3, 4]), **kw)
+    close(out[:300], linear_attention_reference(seqs[0], H, dk, dv, decay, False, 0, 0, dk ** -0.5), 2e-5, "0")
+    close(out[301:430], linear_attention_reference(seqs[2], H, dk, dv, decay, False, 0, 0, dk ** -0.5), 2e-5, "2")
+    ref4 = linear_attention_reference(seqs[4], H, dk, dv, decay, False, 0, 0, dk ** -0.5)
+    close(first[:40], ref4[:40], 2e-5, "4, first step")
+    close(out[431:], ref4[40:], 2e-5, "4, continued")
+    ref1 = linear_attention_reference(torch.cat([rnd(7, width, seed=30), seqs[1]]), H, dk, dv, decay, False, 0, 0, dk ** -0.5)
+    close(out[300:301], ref1[7:], 2e-5, "1")
 
 
 def test_linear_attention_keeps_a_key_from_far_away(ops):
@@ -133,7 +165,7 @@ def test_linear_attention_keeps_a_key_from_far_away(ops):
     outs = [ops.decay_linear_attention(proj[:50].cuda(), step=batch([50], [0], [1]), **kw)]
     for t in range(50, T):
         outs.append(ops.decay_linear_attention(proj[t : t + 1].cuda(), step=batch([1], [t], [1]), **kw))
-    assert torch.equal(torch.cat(outs), got)
+    close(torch.cat(outs), ref, 2e-5, "token by token")
 
 
 @pytest.mark.parametrize("N,group,weighted,gate", [(96, 32, False, "silu"), (80, 80, True, "sigmoid"),
