@@ -303,10 +303,22 @@ __device__ __forceinline__ int chunk_base(const int* cu_q, int seq, int L) {
   return base;
 }
 
+__device__ __forceinline__ void la_copy(float* smem, const float* gmem, bool wide) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+  if (wide) asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"(addr), "l"(gmem));
+  else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(addr), "l"(gmem));
+}
+
+// The rows of a tile go from global to shared memory as they are (cp.async, the next tile while
+// this one is computed: two buffers); activation, rotation and the key's scale are then applied
+// in place. Row i of a token's q (or k) lies at (i / RPT) * (RPT + PAD) + i % RPT: the pad keeps
+// the 16-byte reads of the P lanes of a column on different banks.
+template <int P>
 __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(const LinAttnArgs a) {
-  extern __shared__ float la_smem[];
+  extern __shared__ __align__(16) float la_smem[];
   pdl_trigger();
-  const int P = a.P, CB = a.CB, dk = a.dk, dv = a.dv, H = a.H, L = a.L;
+  constexpr int CB = LA_THREADS / P;
+  const int dk = a.dk, dv = a.dv, H = a.H, L = a.L;
   const int slices = (dv + CB - 1) / CB;
   const int h = blockIdx.x / slices, cb = blockIdx.x - h * slices;
   const int seq = blockIdx.z;
@@ -322,10 +334,8 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
   const int t_begin = c * L, t_end = min(n, t_begin + L);
   const int p = threadIdx.x % P, jl = threadIdx.x / P;
   const int j = cb * CB + jl;
-  const int ldq = P * (LA_RPT + LA_PAD);
-  float* qs = la_smem;                  // [TT][ldq]
-  float* ks = qs + LA_TT * ldq;         // [TT][ldq]
-  float* vs = ks + LA_TT * ldq;         // [TT][CB]
+  constexpr int ldq = P * (LA_RPT + LA_PAD);
+  constexpr int per_buf = 2 * LA_TT * ldq + LA_TT * CB;  // q [TT][ldq], k [TT][ldq], v [TT][CB]
   const float decay = a.decay[h];
   float S[LA_RPT];
   const size_t column = ((size_t)h * dv + (j < dv ? j : 0)) * dk + p * LA_RPT;
@@ -333,7 +343,37 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
   float* st = a.state + (size_t)a.slots[seq] * per_state + column;
   float* chunk_states = nullptr;
   if (num_chunks > 1) chunk_states = a.chunks + (size_t)chunk_base(a.cu_q, seq, L) * per_state + column;
+  // rows beyond key_dim and columns beyond value_dim stay zero in both buffers
+  for (int i = threadIdx.x; i < 2 * per_buf; i += LA_THREADS) la_smem[i] = 0.f;
+  const int cols = min(CB, dv - cb * CB);  // value columns of this block
+  const bool wide_qk = (dk % 4 == 0) && (a.stride % 4 == 0);
+  const bool wide_v = wide_qk && (dv % 4 == 0) && (CB % 4 == 0);
+  const int qk_step = wide_qk ? 4 : 1, v_step = wide_v ? 4 : 1;
+  const int qk_units = dk / qk_step, v_units = (cols + v_step - 1) / v_step;  // cols % 4 == 0 when wide
+  __syncthreads();
   pdl_wait();
+  auto issue = [&](int buf, int t0) {
+    float* qs = la_smem + buf * per_buf;
+    float* ks = qs + LA_TT * ldq;
+    float* vs = ks + LA_TT * ldq;
+    const int tn = min(LA_TT, t_end - t0);
+    for (int idx = threadIdx.x; idx < tn * qk_units; idx += LA_THREADS) {
+      const int tt = idx / qk_units, i = (idx - tt * qk_units) * qk_step;
+      const float* row = a.proj + (size_t)(r0 + t0 + tt) * a.stride + (size_t)h * dk + i;
+      const int at = tt * ldq + (i / LA_RPT) * (LA_RPT + LA_PAD) + (i % LA_RPT);
+      la_copy(qs + at, row, wide_qk);
+      if (!add_pass) la_copy(ks + at, row + (size_t)H * dk, wide_qk);
+    }
+    if (!add_pass)
+      for (int idx = threadIdx.x; idx < tn * v_units; idx += LA_THREADS) {
+        const int tt = idx / v_units, cc = (idx - tt * v_units) * v_step;
+        la_copy(vs + tt * CB + cc,
+                a.proj + (size_t)(r0 + t0 + tt) * a.stride + (size_t)2 * H * dk + (size_t)h * dv + cb * CB + cc,
+                wide_v);
+      }
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+  issue(0, t_begin);
   {
     const float* from = add_pass ? chunk_states + (size_t)(c - 1) * per_state : st;
     const bool read = add_pass || (c == 0 && pos0 > 0);
@@ -341,58 +381,68 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
     for (int r = 0; r < LA_RPT; ++r) S[r] = (read && j < dv && p * LA_RPT + r < dk) ? from[r] : 0.f;
   }
   const int half = a.rot / 2;
+  const int work = dk - half;  // a rotated pair is one piece of work, every other row one
   float carried = 1.f;  // launch C: decay^(tokens of the chunk so far)
-  for (int t0 = t_begin; t0 < t_end; t0 += LA_TT) {
+  int buf = 0;
+  for (int t0 = t_begin; t0 < t_end; t0 += LA_TT, buf ^= 1) {
     const int tn = min(LA_TT, t_end - t0);
+    if (t0 + LA_TT < t_end) {
+      issue(buf ^ 1, t0 + LA_TT);
+      asm volatile("cp.async.wait_group 1;\n" ::);
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::);
+    }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < tn * P * LA_RPT; idx += LA_THREADS) {
-      const int tt = idx / (P * LA_RPT), i = idx - tt * (P * LA_RPT);
-      float q = 0.f, k = 0.f;
-      if (i < dk) {
-        const float* row = a.proj + (size_t)(r0 + t0 + tt) * a.stride + (size_t)h * dk;
-        const float* krow = row + (size_t)H * dk;
-        q = row[i];
-        k = add_pass ? 0.f : krow[i];
+    float* qs = la_smem + buf * per_buf;
+    float* ks = qs + LA_TT * ldq;
+    float* vs = ks + LA_TT * ldq;
+    if (a.silu || a.rot || a.key_scale != 1.f) {
+      for (int idx = threadIdx.x; idx < tn * work; idx += LA_THREADS) {
+        const int tt = idx / work, w = idx - tt * work;
+        const int i = w < half ? w : w + half;  // rows [half, rot) are done with their partners
+        const int at = tt * ldq + (i / LA_RPT) * (LA_RPT + LA_PAD) + (i % LA_RPT);
+        float q = qs[at], k = ks[at];
         if (a.silu) {
           q = silu_f(q);
           k = silu_f(k);
         }
-        if (i < a.rot) {
-          const int f = i < half ? i : i - half;
-          const size_t at = (size_t)(pos0 + t0 + tt) * half + f;
-          const float cs = a.cos[at], sn = a.sin[at];
-          const int ip = i < half ? i + half : i - half;
-          float qp = row[ip], kp = add_pass ? 0.f : krow[ip];
+        if (w < half) {
+          const int ip = i + half;
+          const int atp = tt * ldq + (ip / LA_RPT) * (LA_RPT + LA_PAD) + (ip % LA_RPT);
+          float qp = qs[atp], kp = ks[atp];
           if (a.silu) {
             qp = silu_f(qp);
             kp = silu_f(kp);
           }
-          q = i < half ? q * cs - qp * sn : q * cs + qp * sn;
-          k = i < half ? k * cs - kp * sn : k * cs + kp * sn;
+          const size_t tab = (size_t)(pos0 + t0 + tt) * half + i;
+          const float cs = a.cos[tab], sn = a.sin[tab];
+          qs[atp] = qp * cs + q * sn;
+          ks[atp] = (kp * cs + k * sn) * a.key_scale;
+          const float q2 = q * cs - qp * sn, k2 = k * cs - kp * sn;
+          q = q2;
+          k = k2;
         }
-        k *= a.key_scale;
+        qs[at] = q;
+        ks[at] = k * a.key_scale;
       }
-      const int at = tt * ldq + (i / LA_RPT) * (LA_RPT + LA_PAD) + (i % LA_RPT);
-      qs[at] = q;
-      ks[at] = k;
+      if (a.silu && !add_pass)
+        for (int idx = threadIdx.x; idx < tn * cols; idx += LA_THREADS) {
+          const int tt = idx / cols, cc = idx - tt * cols;
+          vs[tt * CB + cc] = silu_f(vs[tt * CB + cc]);
+        }
+      __syncthreads();
     }
-    if (!add_pass)
-      for (int idx = threadIdx.x; idx < tn * CB; idx += LA_THREADS) {
-        const int tt = idx / CB, cc = idx - tt * CB;
-        float v = 0.f;
-        if (cb * CB + cc < dv) {
-          v = a.proj[(size_t)(r0 + t0 + tt) * a.stride + (size_t)2 * H * dk + (size_t)h * dv + cb * CB + cc];
-          if (a.silu) v = silu_f(v);
-        }
-        vs[idx] = v;
-      }
-    __syncthreads();
-    for (int tt = 0; tt < tn; ++tt) {
-      const float4* q4 = reinterpret_cast<const float4*>(qs + tt * ldq + p * (LA_RPT + LA_PAD));
+    const float4* q4 = reinterpret_cast<const float4*>(qs + p * (LA_RPT + LA_PAD));
+    const float4* k4 = reinterpret_cast<const float4*>(ks + p * (LA_RPT + LA_PAD));
+    const float* vcol = vs + jl;
+    float* dst = a.out + (size_t)(r0 + t0) * ((size_t)H * dv) + (size_t)h * dv + j;
+    const size_t out_stride = (size_t)H * dv;
+    const bool writes = p == 0 && j < dv;
+#pragma unroll 2
+    for (int tt = 0; tt < tn; ++tt, q4 += ldq / 4, k4 += ldq / 4, vcol += CB, dst += out_stride) {
       float acc = 0.f;
       if (!add_pass) {
-        const float vj = vs[tt * CB + jl];
-        const float4* k4 = reinterpret_cast<const float4*>(ks + tt * ldq + p * (LA_RPT + LA_PAD));
+        const float vj = *vcol;
 #pragma unroll
         for (int r4 = 0; r4 < LA_RPT / 4; ++r4) {
           const float4 q = q4[r4], k = k4[r4];
@@ -406,22 +456,28 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
           acc = fmaf(S[4 * r4 + 3], q.w, acc);
         }
       } else {
+        float acc2 = 0.f;
 #pragma unroll
         for (int r4 = 0; r4 < LA_RPT / 4; ++r4) {
           const float4 q = q4[r4];
           acc = fmaf(S[4 * r4 + 0], q.x, acc);
-          acc = fmaf(S[4 * r4 + 1], q.y, acc);
+          acc2 = fmaf(S[4 * r4 + 1], q.y, acc2);
           acc = fmaf(S[4 * r4 + 2], q.z, acc);
-          acc = fmaf(S[4 * r4 + 3], q.w, acc);
+          acc2 = fmaf(S[4 * r4 + 3], q.w, acc2);
         }
+        acc += acc2;
         carried *= decay;
       }
+#pragma unroll
       for (int o = P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (p == 0 && j < dv) {
-        float* dst = a.out + (size_t)(r0 + t0 + tt) * ((size_t)H * dv) + (size_t)h * dv + j;
-        *dst = add_pass ? *dst + carried * acc : acc;
+      if (writes) {
+        // launch C adds into what launch A stored: a reduction without a return value, so that
+        // the warp does not wait for the old value (one thread per element: the order is fixed)
+        if (add_pass) atomicAdd(dst, carried * acc);
+        else *dst = acc;
       }
     }
+    __syncthreads();  // the buffer is free for the tile after the next
   }
   if (add_pass || j >= dv) return;
   float* to = num_chunks > 1 ? chunk_states + (size_t)c * per_state : st;
@@ -449,10 +505,19 @@ __global__ void chain_chunk_states_kernel(float* __restrict__ chunks, float* __r
   const float whole = powf(d, (float)L);
   pdl_wait();
   float S = mine[0];
-  for (int c = 1; c < num_chunks; ++c) {
-    const int len = min(L, n - c * L);
-    S = fmaf(len == L ? whole : powf(d, (float)len), S, mine[(size_t)c * per_state]);
-    mine[(size_t)c * per_state] = S;
+  for (int c0 = 1; c0 < num_chunks; c0 += 8) {  // a round's loads are all in flight before its chain
+    float E[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) E[u] = c0 + u < num_chunks ? __ldcg(mine + (size_t)(c0 + u) * per_state) : 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int c = c0 + u;
+      if (c < num_chunks) {
+        const int len = min(L, n - c * L);
+        S = fmaf(len == L ? whole : powf(d, (float)len), S, E[u]);
+        mine[(size_t)c * per_state] = S;
+      }
+    }
   }
   state[(size_t)slots[seq] * per_state + e] = S;
 }
@@ -576,17 +641,28 @@ extern "C" int lse_decay_linear_attention(const float* proj, long long stride, f
   a.dv = dv; a.rot = rot; a.silu = silu; a.key_scale = key_scale;
   a.P = pow2_at_least((dk + LA_RPT - 1) / LA_RPT);
   a.CB = LA_THREADS / a.P;
+  void (*kernel)(LinAttnArgs) = a.P == 1 ? decay_linear_attention_kernel<1>
+                                : a.P == 2 ? decay_linear_attention_kernel<2>
+                                : a.P == 4 ? decay_linear_attention_kernel<4>
+                                : a.P == 8 ? decay_linear_attention_kernel<8>
+                                           : decay_linear_attention_kernel<16>;
   a.L = lse_linear_attention_chunk();
   a.phase = 0;
   const int slices = (dv + a.CB - 1) / a.CB;
-  const size_t smem = ((size_t)2 * LA_TT * a.P * (LA_RPT + LA_PAD) + (size_t)LA_TT * a.CB) * sizeof(float);
-  launch(decay_linear_attention_kernel, dim3(H * slices, max_chunks, num_seqs), LA_THREADS, smem, stream, a);
+  const size_t smem = 2 * ((size_t)2 * LA_TT * a.P * (LA_RPT + LA_PAD) + (size_t)LA_TT * a.CB) * sizeof(float);
+  static bool configured[17] = {};
+  if (!configured[a.P]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess)
+      return LSE_LAUNCH_FAILED;
+    configured[a.P] = true;
+  }
+  launch(kernel, dim3(H * slices, max_chunks, num_seqs), LA_THREADS, smem, stream, a);
   if (max_chunks > 1) {
     const size_t per_state = (size_t)H * dv * dk;
     launch(chain_chunk_states_kernel, dim3((unsigned)((per_state + 255) / 256), num_seqs), 256, 0, stream,
            chunks, state, decay, cu_q, slots, H, dv, dk, a.L);
     a.phase = 2;
-    launch(decay_linear_attention_kernel, dim3(H * slices, max_chunks - 1, num_seqs), LA_THREADS, smem, stream, a);
+    launch(kernel, dim3(H * slices, max_chunks - 1, num_seqs), LA_THREADS, smem, stream, a);
   }
   return LSE_CHECK_LAUNCH();
 }
