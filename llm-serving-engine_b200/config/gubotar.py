@@ -5,7 +5,7 @@ the epsilon of every norm (``norm.eps``) and a list ``layers``. Each entry of th
 ``type`` (which mixer the layer has), the mixer's sizes and constants under ``mixer`` and its
 feed-forward under ``mlp`` (``{"kind": "dense", "ff": F}`` or null). Layers may differ from one
 another in every size. Nothing has a default: a key that is absent is an error, and so is a key
-this engine does not know, because it would change the math silently.
+of a layer that this engine does not know, because it would change the math silently.
 
 Mixers:
 
@@ -143,6 +143,19 @@ class GubotarConfig:
     @property
     def num_hidden_layers(self) -> int:
         return len(self.layers)
+
+    def num_parameters(self) -> int:
+        """Every checkpoint tensor once (the embedding table is also the output projection)."""
+        from ..models.gubotar import gubotar_checkpoint_layout
+
+        total = 0
+        for entry in gubotar_checkpoint_layout(self).entries:
+            for src in entry.sources:
+                n = 1
+                for k in src.shape:
+                    n *= k
+                total += n
+        return total
 
     @classmethod
     def from_dict(cls, d: dict[str, Any]) -> "GubotarConfig":

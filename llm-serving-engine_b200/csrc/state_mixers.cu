@@ -343,9 +343,11 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
   float* st = a.state + (size_t)a.slots[seq] * per_state + column;
   float* chunk_states = nullptr;
   if (num_chunks > 1) chunk_states = a.chunks + (size_t)chunk_base(a.cu_q, seq, L) * per_state + column;
-  // rows beyond key_dim and columns beyond value_dim stay zero in both buffers
-  for (int i = threadIdx.x; i < 2 * per_buf; i += LA_THREADS) la_smem[i] = 0.f;
+  // rows beyond key_dim and columns beyond value_dim stay zero in both buffers (nothing else is
+  // ever read that the copies below do not write)
   const int cols = min(CB, dv - cb * CB);  // value columns of this block
+  if (dk != P * LA_RPT || cols != CB)
+    for (int i = threadIdx.x; i < 2 * per_buf; i += LA_THREADS) la_smem[i] = 0.f;
   const bool wide_qk = (dk % 4 == 0) && (a.stride % 4 == 0);
   const bool wide_v = wide_qk && (dv % 4 == 0) && (CB % 4 == 0);
   const int qk_step = wide_qk ? 4 : 1, v_step = wide_v ? 4 : 1;
@@ -376,9 +378,18 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
   issue(0, t_begin);
   {
     const float* from = add_pass ? chunk_states + (size_t)(c - 1) * per_state : st;
-    const bool read = add_pass || (c == 0 && pos0 > 0);
+    const bool read = (add_pass || (c == 0 && pos0 > 0)) && j < dv;
+    if (read && dk % 4 == 0) {  // a thread's rows are contiguous: 16-byte loads
 #pragma unroll
-    for (int r = 0; r < LA_RPT; ++r) S[r] = (read && j < dv && p * LA_RPT + r < dk) ? from[r] : 0.f;
+      for (int r4 = 0; r4 < LA_RPT / 4; ++r4) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (p * LA_RPT + 4 * r4 < dk) v = __ldcg(reinterpret_cast<const float4*>(from) + r4);
+        S[4 * r4 + 0] = v.x; S[4 * r4 + 1] = v.y; S[4 * r4 + 2] = v.z; S[4 * r4 + 3] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < LA_RPT; ++r) S[r] = (read && p * LA_RPT + r < dk) ? from[r] : 0.f;
+    }
   }
   const int half = a.rot / 2;
   const int work = dk - half;  // a rotated pair is one piece of work, every other row one
@@ -481,9 +492,16 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
   }
   if (add_pass || j >= dv) return;
   float* to = num_chunks > 1 ? chunk_states + (size_t)c * per_state : st;
+  if (dk % 4 == 0) {
 #pragma unroll
-  for (int r = 0; r < LA_RPT; ++r)
-    if (p * LA_RPT + r < dk) to[r] = S[r];
+    for (int r4 = 0; r4 < LA_RPT / 4; ++r4)
+      if (p * LA_RPT + 4 * r4 < dk)
+        reinterpret_cast<float4*>(to)[r4] = make_float4(S[4 * r4], S[4 * r4 + 1], S[4 * r4 + 2], S[4 * r4 + 3]);
+  } else {
+#pragma unroll
+    for (int r = 0; r < LA_RPT; ++r)
+      if (p * LA_RPT + r < dk) to[r] = S[r];
+  }
 }
 
 // Launch B: one thread per element of the state and sequence of more than one chunk.
