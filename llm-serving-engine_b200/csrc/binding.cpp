@@ -49,6 +49,16 @@ void check_f32(const Tensor& t, const char* what) {
   TORCH_CHECK(t.scalar_type() == torch::kFloat32, what, " must be float32");
 }
 
+// A per-request state is a slice of a [layers, slots, ...] tensor: its start follows from the
+// state's size, so only what the kernels need of it is asked (they read states element by
+// element unless every row of a state is a whole number of 16-byte vectors).
+void check_state(const Tensor& t, const char* what, int64_t vector_rows) {
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == torch::kFloat32, what,
+              " must be a contiguous float32 CUDA tensor");
+  TORCH_CHECK(vector_rows % 4 != 0 || reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0, what,
+              " must start on a 16-byte boundary");
+}
+
 cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
 
 void done(int code, const char* what) {
@@ -404,7 +414,7 @@ void token_shift(const Tensor& x, const Tensor& mix, Tensor& state, Tensor& out,
                  const Tensor& cu_q, const Tensor& ctx_lens, const Tensor& slots) {
   check_f32(x, "x");
   check_f32(mix, "mix");
-  check_f32(state, "state");
+  check_state(state, "state", 1);
   check_cuda(out, "out");
   check_i32(token_seq, "token_seq");
   check_i32(cu_q, "cu_q");
@@ -543,7 +553,7 @@ void decay_linear_attention(const Tensor& proj, Tensor& out, Tensor& state, cons
                             int64_t max_chunks, const OptTensor& chunks) {
   check_f32(proj, "proj");
   check_f32(out, "out");
-  check_f32(state, "state");
+  check_state(state, "state", dk);
   check_f32(decay, "decay");
   check_i32(cu_q, "cu_q");
   check_i32(ctx_lens, "ctx_lens");

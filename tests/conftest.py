@@ -113,6 +113,13 @@ GUBOTAR_TINY = {
         "architecture": "Gubotar", "vocab": 130, "width": 68, "norm": {"eps": 1e-6},
         "layers": [_par(2, 1, 40, 0.35, 7, 1, 20, 64, [0.95], 96),
                    _par(6, 6, 16, 0.5, 33, 4, 8, 8, [0.9, 0.99, 0.999, 0.3], 48)]}),
+    # sizes that are multiples of nothing: width 70, head sizes 24, 10, 12 and 20, six rotated dims
+    # of ten, four query heads on one key head, a chunk of one page, a single layer kind first
+    "G3": dict(seed=14, page_tokens=16, config={
+        "architecture": "Gubotar", "vocab": 97, "width": 70, "norm": {"eps": 1e-5},
+        "layers": [_par(4, 1, 24, 0.4, 16, 3, 12, 20, [0.97, 0.9, 0.999], 50),
+                   _ret(5, 10, 14, [0.9, 0.95, 0.99, 0.995, 0.999], 6, 777.0, 0),
+                   _par(2, 2, 32, 0.2, 1, 2, 10, 36, [0.5, 0.9], 30)]}),
 }
 
 
