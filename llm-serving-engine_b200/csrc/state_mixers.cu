@@ -257,7 +257,8 @@ __global__ void norm_rope_kv_write_kernel(const float* __restrict__ qkv, T* __re
 // ------------------------------------------------------------------------------------ linear attention with decay
 // S_t = decay * S_{t-1} + k_t v_t^T,  o_t = S_t^T q_t, in float32 on the CUDA cores.
 // One block per (head, slice of CB value columns, chunk of the portion, sequence); 256 threads.
-// A column of S (key_dim values) is shared by P neighbouring lanes, RPT = 16 rows each, held in
+// A pair of neighbouring columns of S (key_dim values each) is shared by P neighbouring lanes,
+// RPT = 8 rows of both columns each (so a thread's q and k values serve two columns), held in
 // registers while the block steps through its tokens; the P partial dot products of o are added
 // with shuffles. Columns are independent of one another, so slices of a head's columns run as
 // separate blocks. q, k (after activation, rotation and scaling) and v of TT tokens are staged in
@@ -272,7 +273,7 @@ __global__ void norm_rope_kv_write_kernel(const float* __restrict__ qkv, T* __re
 //   C  chunk c >= 1 adds what the state before it contributes: o_t += decay^(t - t_c + 1) F_{c-1}^T q_t.
 // A portion of at most L tokens (a single token, above all) is one chunk: launch A alone, which
 // then reads and writes the request's state itself.
-constexpr int LA_RPT = 16, LA_TT = 16, LA_THREADS = 256, LA_PAD = 4;
+constexpr int LA_RPT = 8, LA_TT = 16, LA_THREADS = 256, LA_PAD = 4;
 
 struct LinAttnArgs {
   const float* proj;      // [T, stride]: q | k | v | ... per row, heads concatenated
@@ -317,7 +318,7 @@ template <int P>
 __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(const LinAttnArgs a) {
   extern __shared__ __align__(16) float la_smem[];
   pdl_trigger();
-  constexpr int CB = LA_THREADS / P;
+  constexpr int CB = 2 * LA_THREADS / P;
   const int dk = a.dk, dv = a.dv, H = a.H, L = a.L;
   const int slices = (dv + CB - 1) / CB;
   const int h = blockIdx.x / slices, cb = blockIdx.x - h * slices;
@@ -332,13 +333,14 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
   }
   const int pos0 = a.ctx_lens[seq] - n;
   const int t_begin = c * L, t_end = min(n, t_begin + L);
-  const int p = threadIdx.x % P, jl = threadIdx.x / P;
-  const int j = cb * CB + jl;
+  const int p = threadIdx.x % P, jl = 2 * (threadIdx.x / P);
+  const int j = cb * CB + jl;  // this thread's columns: j and j + 1
   constexpr int ldq = P * (LA_RPT + LA_PAD);
   constexpr int per_buf = 2 * LA_TT * ldq + LA_TT * CB;  // q [TT][ldq], k [TT][ldq], v [TT][CB]
   const float decay = a.decay[h];
-  float S[LA_RPT];
-  const size_t column = ((size_t)h * dv + (j < dv ? j : 0)) * dk + p * LA_RPT;
+  float S[LA_RPT], S1[LA_RPT];
+  const bool has0 = j < dv, has1 = j + 1 < dv;
+  const size_t column = ((size_t)h * dv + (has0 ? j : 0)) * dk + p * LA_RPT;
   const size_t per_state = (size_t)H * dv * dk;
   float* st = a.state + (size_t)a.slots[seq] * per_state + column;
   float* chunk_states = nullptr;
@@ -378,18 +380,22 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
   issue(0, t_begin);
   {
     const float* from = add_pass ? chunk_states + (size_t)(c - 1) * per_state : st;
-    const bool read = (add_pass || (c == 0 && pos0 > 0)) && j < dv;
-    if (read && dk % 4 == 0) {  // a thread's rows are contiguous: 16-byte loads
+    const bool read = add_pass || (c == 0 && pos0 > 0);
+    auto load_column = [&](float (&dst)[LA_RPT], const float* src, bool on) {
+      if (on && dk % 4 == 0) {  // a thread's rows are contiguous: 16-byte loads
 #pragma unroll
-      for (int r4 = 0; r4 < LA_RPT / 4; ++r4) {
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (p * LA_RPT + 4 * r4 < dk) v = __ldcg(reinterpret_cast<const float4*>(from) + r4);
-        S[4 * r4 + 0] = v.x; S[4 * r4 + 1] = v.y; S[4 * r4 + 2] = v.z; S[4 * r4 + 3] = v.w;
+        for (int r4 = 0; r4 < LA_RPT / 4; ++r4) {
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (p * LA_RPT + 4 * r4 < dk) v = __ldcg(reinterpret_cast<const float4*>(src) + r4);
+          dst[4 * r4 + 0] = v.x; dst[4 * r4 + 1] = v.y; dst[4 * r4 + 2] = v.z; dst[4 * r4 + 3] = v.w;
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < LA_RPT; ++r) dst[r] = (on && p * LA_RPT + r < dk) ? src[r] : 0.f;
       }
-    } else {
-#pragma unroll
-      for (int r = 0; r < LA_RPT; ++r) S[r] = (read && p * LA_RPT + r < dk) ? from[r] : 0.f;
-    }
+    };
+    load_column(S, from, read && has0);
+    load_column(S1, from + dk, read && has1);
   }
   const int half = a.rot / 2;
   const int work = dk - half;  // a rotated pair is one piece of work, every other row one
@@ -446,62 +452,79 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
     const float4* q4 = reinterpret_cast<const float4*>(qs + p * (LA_RPT + LA_PAD));
     const float4* k4 = reinterpret_cast<const float4*>(ks + p * (LA_RPT + LA_PAD));
     const float* vcol = vs + jl;
-    float* dst = a.out + (size_t)(r0 + t0) * ((size_t)H * dv) + (size_t)h * dv + j;
+    // after the reduction lane p == 0 holds column j's sum and lane p == 1 column j + 1's
+    const int mine = P > 1 ? (p & 1) : 0;
+    float* dst = a.out + (size_t)(r0 + t0) * ((size_t)H * dv) + (size_t)h * dv + j + mine;
     const size_t out_stride = (size_t)H * dv;
-    const bool writes = p == 0 && j < dv;
+    const bool writes = P > 1 ? (p < 2 && j + mine < dv) : has0;
 #pragma unroll 2
     for (int tt = 0; tt < tn; ++tt, q4 += ldq / 4, k4 += ldq / 4, vcol += CB, dst += out_stride) {
-      float acc = 0.f;
+      float acc0 = 0.f, acc1 = 0.f;
       if (!add_pass) {
-        const float vj = *vcol;
+        const float2 vj = *reinterpret_cast<const float2*>(vcol);
 #pragma unroll
         for (int r4 = 0; r4 < LA_RPT / 4; ++r4) {
           const float4 q = q4[r4], k = k4[r4];
-          S[4 * r4 + 0] = fmaf(decay, S[4 * r4 + 0], k.x * vj);
-          S[4 * r4 + 1] = fmaf(decay, S[4 * r4 + 1], k.y * vj);
-          S[4 * r4 + 2] = fmaf(decay, S[4 * r4 + 2], k.z * vj);
-          S[4 * r4 + 3] = fmaf(decay, S[4 * r4 + 3], k.w * vj);
-          acc = fmaf(S[4 * r4 + 0], q.x, acc);
-          acc = fmaf(S[4 * r4 + 1], q.y, acc);
-          acc = fmaf(S[4 * r4 + 2], q.z, acc);
-          acc = fmaf(S[4 * r4 + 3], q.w, acc);
+          const float qv[4] = {q.x, q.y, q.z, q.w}, kv[4] = {k.x, k.y, k.z, k.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            S[4 * r4 + e] = fmaf(decay, S[4 * r4 + e], kv[e] * vj.x);
+            S1[4 * r4 + e] = fmaf(decay, S1[4 * r4 + e], kv[e] * vj.y);
+            acc0 = fmaf(S[4 * r4 + e], qv[e], acc0);
+            acc1 = fmaf(S1[4 * r4 + e], qv[e], acc1);
+          }
         }
       } else {
-        float acc2 = 0.f;
 #pragma unroll
         for (int r4 = 0; r4 < LA_RPT / 4; ++r4) {
           const float4 q = q4[r4];
-          acc = fmaf(S[4 * r4 + 0], q.x, acc);
-          acc2 = fmaf(S[4 * r4 + 1], q.y, acc2);
-          acc = fmaf(S[4 * r4 + 2], q.z, acc);
-          acc2 = fmaf(S[4 * r4 + 3], q.w, acc2);
+          const float qv[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            acc0 = fmaf(S[4 * r4 + e], qv[e], acc0);
+            acc1 = fmaf(S1[4 * r4 + e], qv[e], acc1);
+          }
         }
-        acc += acc2;
         carried *= decay;
       }
+      float acc = acc0;
+      if (P > 1) {
+        // the first step halves the data: a lane hands over the sum of the column it does not keep
+        const float give = mine ? acc0 : acc1, keep = mine ? acc1 : acc0;
+        acc = keep + __shfl_xor_sync(0xffffffffu, give, 1);
 #pragma unroll
-      for (int o = P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        for (int o = P >> 1; o > 1; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      }
       if (writes) {
         // launch C adds into what launch A stored: a reduction without a return value, so that
         // the warp does not wait for the old value (one thread per element: the order is fixed)
         if (add_pass) atomicAdd(dst, carried * acc);
         else *dst = acc;
       }
+      if (P == 1 && has1) {
+        if (add_pass) atomicAdd(dst + 1, carried * acc1);
+        else dst[1] = acc1;
+      }
     }
     __syncthreads();  // the buffer is free for the tile after the next
   }
-  if (add_pass || j >= dv) return;
+  if (add_pass) return;
   float* to = num_chunks > 1 ? chunk_states + (size_t)c * per_state : st;
-  if (dk % 4 == 0) {
+  auto store_column = [&](const float (&src)[LA_RPT], float* dst) {
+    if (dk % 4 == 0) {
 #pragma unroll
-    for (int r4 = 0; r4 < LA_RPT / 4; ++r4)
-      if (p * LA_RPT + 4 * r4 < dk)
-        reinterpret_cast<float4*>(to)[r4] = make_float4(S[4 * r4], S[4 * r4 + 1], S[4 * r4 + 2], S[4 * r4 + 3]);
-  } else {
+      for (int r4 = 0; r4 < LA_RPT / 4; ++r4)
+        if (p * LA_RPT + 4 * r4 < dk)
+          reinterpret_cast<float4*>(dst)[r4] =
+              make_float4(src[4 * r4], src[4 * r4 + 1], src[4 * r4 + 2], src[4 * r4 + 3]);
+    } else {
 #pragma unroll
-    for (int r = 0; r < LA_RPT; ++r)
-      if (p * LA_RPT + r < dk) to[r] = S[r];
-  }
+      for (int r = 0; r < LA_RPT; ++r)
+        if (p * LA_RPT + r < dk) dst[r] = src[r];
+    }
+  };
+  if (has0) store_column(S, to);
+  if (has1) store_column(S1, to + dk);
 }
 
 // Launch B: one thread per element of the state and sequence of more than one chunk.
@@ -658,19 +681,20 @@ extern "C" int lse_decay_linear_attention(const float* proj, long long stride, f
   a.cu_q = cu_q; a.ctx_lens = ctx_lens; a.slots = slots; a.cos = cos; a.sin = sin; a.H = H; a.dk = dk;
   a.dv = dv; a.rot = rot; a.silu = silu; a.key_scale = key_scale;
   a.P = pow2_at_least((dk + LA_RPT - 1) / LA_RPT);
-  a.CB = LA_THREADS / a.P;
+  a.CB = 2 * LA_THREADS / a.P;
   void (*kernel)(LinAttnArgs) = a.P == 1 ? decay_linear_attention_kernel<1>
                                 : a.P == 2 ? decay_linear_attention_kernel<2>
                                 : a.P == 4 ? decay_linear_attention_kernel<4>
                                 : a.P == 8 ? decay_linear_attention_kernel<8>
-                                           : decay_linear_attention_kernel<16>;
+                                : a.P == 16 ? decay_linear_attention_kernel<16>
+                                            : decay_linear_attention_kernel<32>;
   a.L = lse_linear_attention_chunk();
   a.phase = 0;
   const int slices = (dv + a.CB - 1) / a.CB;
   const size_t smem = 2 * ((size_t)2 * LA_TT * a.P * (LA_RPT + LA_PAD) + (size_t)LA_TT * a.CB) * sizeof(float);
-  static bool configured[17] = {};
+  static bool configured[33] = {};
   if (!configured[a.P]) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess)
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024) != cudaSuccess)
       return LSE_LAUNCH_FAILED;
     configured[a.P] = true;
   }
