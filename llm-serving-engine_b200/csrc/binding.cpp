@@ -443,16 +443,20 @@ const float* opt_f32(const OptTensor& t, int64_t n, const char* what) {
 void rmsnorm_add(Tensor& x, const Tensor& a, const OptTensor& b, const OptTensor& wa, const OptTensor& wb,
                  double ca, double cb, double eps_in, const Tensor& w, double eps, const OptTensor& out) {
   check_f32(x, "x");
-  check_f32(a, "a");
+  check_cuda(a, "a");
   check_f32(w, "w");
   TORCH_CHECK(x.dim() == 2 && a.sizes() == x.sizes() && w.numel() == x.size(1), "rmsnorm_add: bad shapes");
+  const int branch_code = dtype_code(a, "a");  // float32, or the fixed-point sums of a few-rows product
+  TORCH_CHECK(branch_code == LSE_F32 || branch_code == LSE_FIXED64, "rmsnorm_add: a must be float32 or sums");
   const int64_t H = x.size(1);
-  const float* bp = nullptr;
+  const void* bp = nullptr;
   if (b) {
-    check_f32(*b, "b");
+    check_cuda(*b, "b");
     TORCH_CHECK(b->sizes() == x.sizes() && wa && wb, "rmsnorm_add: a second branch needs its shape and both weights");
-    bp = b->data_ptr<float>();
+    TORCH_CHECK(b->scalar_type() == a.scalar_type(), "rmsnorm_add: both branches must be of one kind");
+    bp = b->data_ptr();
   }
+  TORCH_CHECK(branch_code == LSE_F32 || H * (b ? 2 : 1) * 4 <= 48 * 1024, "rmsnorm_add: rows of sums are too long");
   void* op = nullptr;
   int oc = LSE_F32;
   if (out) {
@@ -461,7 +465,7 @@ void rmsnorm_add(Tensor& x, const Tensor& a, const OptTensor& b, const OptTensor
     op = out->data_ptr();
     oc = out_code(*out, "out");
   }
-  done(lse_rmsnorm_add(x.data_ptr<float>(), a.data_ptr<float>(), bp, opt_f32(wa, H, "wa"), opt_f32(wb, H, "wb"),
+  done(lse_rmsnorm_add(x.data_ptr<float>(), a.data_ptr(), bp, branch_code, opt_f32(wa, H, "wa"), opt_f32(wb, H, "wb"),
                        (float)ca, (float)cb, (float)eps_in, w.data_ptr<float>(), (float)eps, op, oc,
                        (int)x.size(0), (int)H, stream()),
        "rmsnorm_add");

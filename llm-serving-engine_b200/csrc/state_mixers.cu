@@ -57,19 +57,40 @@ __global__ void token_shift_kernel(const float* __restrict__ x, const float* __r
 // ------------------------------------------------------------------------------------ x += norm(branch)
 // One block per row. y = a, or, with inner weights, ca * wa * a / rms(a) (+ cb * wb * b / rms(b));
 // then x += w * y / rms(y), and out = x in the compute dtype if out is given. y is recomputed
-// in the last pass rather than kept: the row's second read comes from cache.
-template <typename TO>
-__global__ void rmsnorm_add_kernel(float* __restrict__ x, const float* __restrict__ a,
-                                   const float* __restrict__ b, const float* __restrict__ wa,
+// in the last pass rather than kept: the row's second read comes from cache. SUMS: a (and b) are
+// the fixed-point sums of a few-rows product; they are taken once (converted into shared memory,
+// zeros left behind) and read from there.
+template <typename TO, bool SUMS>
+__global__ void rmsnorm_add_kernel(float* __restrict__ x, const void* a, const void* b,
+                                   const float* __restrict__ wa,
                                    const float* __restrict__ wb, float ca, float cb, float eps_in,
                                    const float* __restrict__ w, float eps, TO* __restrict__ out,
                                    int H) {
   __shared__ float scratch[32];
+  extern __shared__ float taken[];  // SUMS: [H] for a, then [H] for b
   pdl_trigger();
   pdl_wait();
   const size_t row = (size_t)blockIdx.x * H;
-  const float* ar = a + row;
-  const float* br = b ? b + row : nullptr;
+  const float* ar;
+  const float* br = nullptr;
+  if (SUMS) {
+    fixed64* as = reinterpret_cast<fixed64*>(const_cast<void*>(a)) + row;
+    fixed64* bs = b ? reinterpret_cast<fixed64*>(const_cast<void*>(b)) + row : nullptr;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      taken[i] = fixed_to_float(as[i]);
+      as[i] = 0;
+      if (bs) {
+        taken[H + i] = fixed_to_float(bs[i]);
+        bs[i] = 0;
+      }
+    }
+    __syncthreads();
+    ar = taken;
+    if (bs) br = taken + H;
+  } else {
+    ar = reinterpret_cast<const float*>(a) + row;
+    if (b) br = reinterpret_cast<const float*>(b) + row;
+  }
   float inv_a = 1.f, inv_b = 1.f;
   if (wa) {
     float sa = 0.f, sb = 0.f;
@@ -597,19 +618,26 @@ extern "C" int lse_token_shift(const float* x, const float* mix, float* state, v
   return LSE_CHECK_LAUNCH();
 }
 
-extern "C" int lse_rmsnorm_add(float* x, const float* a, const float* b, const float* wa, const float* wb,
-                               float ca, float cb, float eps_in, const float* w, float eps, void* out,
-                               int out_dtype, int T, int H, cudaStream_t stream) {
+extern "C" int lse_rmsnorm_add(float* x, const void* a, const void* b, int branch_dtype, const float* wa,
+                               const float* wb, float ca, float cb, float eps_in, const float* w, float eps,
+                               void* out, int out_dtype, int T, int H, cudaStream_t stream) {
   if (T <= 0) return LSE_OK;
   if (!x || !a || !w || (b && !wa) || (wa && b && !wb)) return LSE_BAD_ARGUMENT;
+  if (branch_dtype != LSE_F32 && branch_dtype != LSE_FIXED64) return LSE_BAD_ARGUMENT;
+  const bool sums = branch_dtype == LSE_FIXED64;
+  const size_t smem = sums ? (size_t)H * (b ? 2 : 1) * sizeof(float) : 0;
+  if (smem > 48 * 1024) return LSE_BAD_ARGUMENT;
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-  if (out && out_dtype == LSE_BF16)
-    launch(rmsnorm_add_kernel<bf16>, T, threads, 0, stream, x, a, b, wa, wb, ca, cb, eps_in, w, eps,
-           (bf16*)out, H);
-  else if (!out || out_dtype == LSE_F32)
-    launch(rmsnorm_add_kernel<float>, T, threads, 0, stream, x, a, b, wa, wb, ca, cb, eps_in, w, eps,
-           (float*)out, H);
-  else return LSE_BAD_ARGUMENT;
+  const bool to_bf16 = out && out_dtype == LSE_BF16;
+  if (!to_bf16 && out && out_dtype != LSE_F32) return LSE_BAD_ARGUMENT;
+#define LSE_RNA(TO, S) \
+  launch(rmsnorm_add_kernel<TO, S>, T, threads, smem, stream, x, a, b, wa, wb, ca, cb, eps_in, w, eps, (TO*)out, H)
+  if (to_bf16) {
+    if (sums) LSE_RNA(bf16, true); else LSE_RNA(bf16, false);
+  } else {
+    if (sums) LSE_RNA(float, true); else LSE_RNA(float, false);
+  }
+#undef LSE_RNA
   return LSE_CHECK_LAUNCH();
 }
 

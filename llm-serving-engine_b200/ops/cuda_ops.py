@@ -52,6 +52,26 @@ class PendingSums:
         return None
 
 
+class DeferredProduct:
+    """A few-rows product whose fixed-point sums nobody has taken yet. What ``linear`` may return
+    to a caller that says ``may_defer=True`` without a tensor to add into: a kernel that reads the
+    product once anyway (``rmsnorm_add``) takes the sums itself; :meth:`resolve` converts them to a
+    float32 tensor for everybody else."""
+
+    __slots__ = ("ops", "sums")
+
+    def __init__(self, ops: "CudaOps", sums: torch.Tensor) -> None:
+        self.ops, self.sums = ops, sums
+
+    def resolve(self) -> torch.Tensor:
+        out = torch.empty(self.sums.shape, dtype=torch.float32, device=self.sums.device)
+        self.ops.ext.fixed_to_float(self.sums, out, False)
+        self.ops.launches += 1
+        self.ops._sums_taken(self.sums)
+        self.sums = None
+        return out
+
+
 # Cost of a block of the single-token attention kernel in units of one key: its start (tables,
 # queries, first tile) and end (partial results, counter), and what each further partition adds
 # to the merge. From timings at 2118 keys of head size 64: a wave of blocks takes about 39 ns per
@@ -116,7 +136,7 @@ class CudaOps:
         self.skinny_max_rows = int(self.ext.gemm_bf16_skinny_max_rows())
         # Fixed-point sum buffers of the few-rows product, by shape. A buffer is zero whenever it
         # is not in _sums_live (the kernel that takes a product's sums leaves zeros behind).
-        self._sums: dict[tuple[int, int], torch.Tensor] = {}
+        self._sums: dict[tuple[int, int], list[torch.Tensor]] = {}
         self._sums_live: set[int] = set()  # data_ptr of buffers whose sums have not been taken yet
         self._addmm_in_place: bool | None = None  # whether torch.addmm can add into a float32 tensor
         self.launches = 0  # kernels of this package enqueued (library matrix products not counted)
@@ -190,11 +210,12 @@ class CudaOps:
         """``a @ w.T (+ bias)`` as fixed-point sums in a buffer that the caller must have taken
         (by a kernel that clears it) before the buffer of this shape is used again."""
         T, N = a.shape[0], w.shape[0]
-        buf = self._sums.get((T, N))
-        if buf is None and not torch.cuda.is_current_stream_capturing():
-            buf = self._sums[(T, N)] = torch.zeros(T, N, dtype=torch.int64, device=self.device)
-        if buf is None or buf.data_ptr() in self._sums_live:
-            buf = torch.zeros(T, N, dtype=torch.int64, device=self.device)  # rare: the shape's buffer is busy
+        kept = self._sums.setdefault((T, N), [])  # usually one; two when branches of one shape are pending together
+        buf = next((b for b in kept if b.data_ptr() not in self._sums_live), None)
+        if buf is None:
+            buf = torch.zeros(T, N, dtype=torch.int64, device=self.device)
+            if not torch.cuda.is_current_stream_capturing():
+                kept.append(buf)
         self._sums_live.add(buf.data_ptr())
         self.ext.gemm_bf16_skinny(a, w, bias, buf)
         self.launches += 1
@@ -242,6 +263,8 @@ class CudaOps:
             if accumulate_into is not None:
                 pending = PendingSums(self, sums, accumulate_into)
                 return pending if may_defer else pending.resolve()
+            if may_defer and out_dtype == torch.float32:
+                return DeferredProduct(self, sums)
             out = torch.empty(T, N, dtype=out_dtype or torch.bfloat16, device=a.device)
             self.ext.fixed_to_float(sums, out, False)
             self.launches += 1
@@ -437,6 +460,7 @@ class CudaOps:
         return branches[0], b, weights[0], wb, float(coefficients[0]), float(cb)
 
     def mix_normed(self, branches, weights, coefficients, eps):
+        branches = [m.resolve() if isinstance(m, DeferredProduct) else m for m in branches]
         a, b, wa, wb, ca, cb = self._two_branches(branches, weights, coefficients)
         out = torch.empty_like(a)
         self.ext.mix_normed(a, b, wa, wb, ca, cb, float(eps), out)
@@ -448,12 +472,23 @@ class CudaOps:
         ``BranchMix`` whose members are normed and summed in the same launch); returns the new
         ``x`` in ``out_dtype`` unless that is None."""
         out = None if out_dtype is None else torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        members = list(branch.branches) if hasattr(branch, "branches") else [branch]
+        # products still lying as sums are taken by the kernel itself if all members are such
+        # and their rows fit its shared memory; otherwise they are converted first
+        deferred = [m for m in members if isinstance(m, DeferredProduct)]
+        take = (len(deferred) == len(members) and all(m.sums is not None for m in deferred)
+                and x.shape[1] * len(members) * 4 <= 48 * 1024)
+        tensors = [(m.sums if take else m.resolve()) if isinstance(m, DeferredProduct) else m for m in members]
         if hasattr(branch, "branches"):
-            a, b, wa, wb, ca, cb = self._two_branches(branch.branches, branch.weights, branch.coefficients)
+            a, b, wa, wb, ca, cb = self._two_branches(tensors, branch.weights, branch.coefficients)
             self.ext.rmsnorm_add(x, a, b, wa, wb, ca, cb, float(branch.eps), weight, float(eps), out)
         else:
-            self.ext.rmsnorm_add(x, branch, None, None, None, 1.0, 0.0, 0.0, weight, float(eps), out)
+            self.ext.rmsnorm_add(x, tensors[0], None, None, None, 1.0, 0.0, 0.0, weight, float(eps), out)
         self.launches += 1
+        if take:
+            for m in deferred:
+                self._sums_taken(m.sums)
+                m.sums = None
         return out
 
     def decay_linear_attention(self, proj, *, num_heads, key_dim, value_dim, decay, state, step,

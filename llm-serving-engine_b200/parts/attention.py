@@ -151,6 +151,7 @@ class PagedAttention(Mixer):
         return {"tiles": tokens // qt + portions, "decode_seqs": single}
 
     accepts_residual = True
+    accepts_deferral = True
 
     def forward(self, h, step, cache, residual=None, may_defer=False):
         s = self.spec

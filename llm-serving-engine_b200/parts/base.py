@@ -284,9 +284,13 @@ class Block(Part):
 
 def project_into(ops, a, w, bias, out_dtype, residual, may_defer: bool = False):
     """A branch's output projection ``a @ w.T (+ bias)``: added into ``residual`` (the float32
-    stream) where one is given. Returns None (added), the product, or pending sums (only if
-    ``may_defer``)."""
+    stream) where one is given. Returns None (added), the product, or, only if ``may_defer``, an
+    object with ``resolve()``: pending sums for ``residual``, or without a residual a product that
+    the kernel set has not converted yet (``Norm.add_normed`` takes either)."""
     if residual is None:
+        if may_defer and getattr(ops, "defers_adds", False):
+            # may be a product whose sums are still to be taken (an object with resolve())
+            return ops.linear(a, w, bias, out_dtype=out_dtype, may_defer=True)
         return ops.linear(a, w, bias, out_dtype=out_dtype)
     if may_defer and getattr(ops, "defers_adds", False):
         return ops.linear(a, w, bias, out_dtype=out_dtype, accumulate_into=residual, may_defer=True)

@@ -106,8 +106,15 @@ class BranchNormBlock(Block):
             h = self.filter.forward(x, step, cache.part(*self._filter_part))
         else:
             h = self.ops.cast(x, self.env.dtype)
-        a = self.mixer.forward(h, step, cache.part(*self._mixer_part))
+        if getattr(self.mixer, "accepts_deferral", False):
+            a = self.mixer.forward(h, step, cache.part(*self._mixer_part), may_defer=True)
+        else:
+            a = self.mixer.forward(h, step, cache.part(*self._mixer_part))
         h = self.norm_mixer.add_normed(x, a, emit=self.feed_forward is not None)
         if self.feed_forward is not None:
-            self.norm_ff.add_normed(x, self.feed_forward.forward(h, step), emit=False)
+            if getattr(self.feed_forward, "accepts_residual", False):
+                f = self.feed_forward.forward(h, step, may_defer=True)
+            else:
+                f = self.feed_forward.forward(h, step)
+            self.norm_ff.add_normed(x, f, emit=False)
         return x, None

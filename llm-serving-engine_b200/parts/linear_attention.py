@@ -28,7 +28,7 @@ from typing import Any
 
 import torch
 
-from .base import MIXERS, POSITION_ENCODINGS, Mixer, ParamDecl, StateNeed
+from .base import MIXERS, POSITION_ENCODINGS, Mixer, ParamDecl, StateNeed, project_into
 
 
 @dataclass(frozen=True)
@@ -90,7 +90,9 @@ class DecayLinearAttention(Mixer):
         s = self.spec
         return StateNeed((s.num_heads, s.value_dim, s.key_dim), torch.float32)
 
-    def forward(self, h, step, cache):
+    accepts_deferral = True  # forward(..., may_defer=True) may return a product not yet converted
+
+    def forward(self, h, step, cache, may_defer=False):
         s, ops = self.spec, self.ops
         proj = ops.linear(h, self.qkvg_weight, None, out_dtype=torch.float32)
         cos, sin = self.rotary if self.rotary is not None else (None, None)
@@ -103,4 +105,4 @@ class DecayLinearAttention(Mixer):
             group=s.value_dim if s.out_norm == "heads" else self.vg,
             weight=self.norm_weight, eps=s.eps, gate_activation=s.gate_activation,
             out_dtype=self.env.dtype)
-        return ops.linear(y, self.o_weight, None, out_dtype=self.env.residual_dtype)
+        return project_into(ops, y, self.o_weight, None, self.env.residual_dtype, None, may_defer)

@@ -59,9 +59,14 @@ class ParallelMixer(Mixer):
     def cache_need(self):
         return tuple(n for b in self.branches for n in flatten_needs(b.cache_need()))
 
-    def forward(self, h, step, cache):
+    accepts_deferral = True
+
+    def forward(self, h, step, cache, may_defer=False):
         outs = []
         for b, (pages, first, n) in zip(self.branches, self._parts):
-            a = b.forward(h, step, cache.part(pages, first, n))
-            outs.append(a.resolve() if hasattr(a, "resolve") else a)
+            defer = may_defer and getattr(b, "accepts_deferral", False)
+            a = (b.forward(h, step, cache.part(pages, first, n), may_defer=True) if defer
+                 else b.forward(h, step, cache.part(pages, first, n)))
+            # a branch's product that is not converted yet stays so only if the caller takes such
+            outs.append(a.resolve() if hasattr(a, "resolve") and not defer else a)
         return BranchMix(self.ops, outs, self.out_weights, tuple(self.spec.coefficients), self.spec.eps)
