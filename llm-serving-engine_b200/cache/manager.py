@@ -225,7 +225,10 @@ class CacheManager:
         return self.pools[group].num_pages
 
     def usage(self) -> float:
+        """Fraction of the pages in use; for a model that keeps no pages, of the state slots."""
         total = sum(p.num_pages for p in self.pools)
+        if total == 0:
+            return 1.0 - len(self.free_slots) / self.max_requests
         return 1.0 - sum(p.num_free for p in self.pools) / total
 
     def check_invariants(self) -> None:

@@ -120,6 +120,10 @@ GUBOTAR_TINY = {
         "layers": [_par(4, 1, 24, 0.4, 16, 3, 12, 20, [0.97, 0.9, 0.999], 50),
                    _ret(5, 10, 14, [0.9, 0.95, 0.99, 0.995, 0.999], 6, 777.0, 0),
                    _par(2, 2, 32, 0.2, 1, 2, 10, 36, [0.5, 0.9], 30)]}),
+    # retention layers only: the model keeps no pages at all; two rotated dims of 32
+    "G4": dict(seed=21, page_tokens=16, config={
+        "architecture": "Gubotar", "vocab": 64, "width": 32, "norm": {"eps": 1e-6},
+        "layers": [_ret(2, 16, 16, [0.9, 0.99], 16, 1e4, 48), _ret(1, 32, 8, [0.95], 2, 1e4, 0)]}),
 }
 
 

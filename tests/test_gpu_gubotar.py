@@ -346,7 +346,7 @@ def gpu_runner(folder, name, num_pages, dtype, max_num_seqs=4, max_len=512):
                        max_model_len=max_len, max_num_seqs=max_num_seqs, max_num_batched_tokens=max_len)
 
 
-LENGTHS = {"G1": [5, 70, 1, 33, 49, 126, 2], "G2": [2, 40, 9, 64, 17, 100], "G3": [3, 50, 18, 77, 130]}
+LENGTHS = {"G1": [5, 70, 1, 33, 49, 126, 2], "G2": [2, 40, 9, 64, 17, 100], "G3": [3, 50, 18, 77, 130], "G4": [5, 70, 33, 100, 1]}
 TOL = {"float32": (0.0, 2e-5), "bfloat16": (0.0, 0.03)}  # (absolute, relative to the largest logit)
 
 
@@ -360,7 +360,7 @@ def expected(gubotar_dirs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["G1", "G2", "G3"])
+@pytest.mark.parametrize("name", ["G1", "G2", "G3", "G4"])
 @pytest.mark.parametrize("mode", ["whole", "decode_tail", "portions", "mixed"])
 def test_every_way_of_cutting_matches_plain(gubotar_dirs, expected, name, mode, dtype):
     reqs, exp = expected[name]

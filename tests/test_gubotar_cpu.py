@@ -76,10 +76,10 @@ def test_a_cache_layer_holds_pages_and_states_side_by_side(gubotar_dirs):
     assert runner.pools.view(0, True).k is None
 
 
-LENGTHS = {"G1": [5, 70, 1, 33, 49, 26], "G2": [2, 40, 9, 64, 17], "G3": [3, 50, 18, 77]}
+LENGTHS = {"G1": [5, 70, 1, 33, 49, 26], "G2": [2, 40, 9, 64, 17], "G3": [3, 50, 18, 77], "G4": [5, 70, 33, 100]}
 
 
-@pytest.mark.parametrize("name", ["G1", "G2", "G3"])
+@pytest.mark.parametrize("name", ["G1", "G2", "G3", "G4"])
 @pytest.mark.parametrize("mode", ["whole", "decode_tail", "portions", "mixed"])
 def test_every_way_of_cutting_matches_plain(gubotar_dirs, name, mode):
     folder = gubotar_dirs[name]
