@@ -1,7 +1,7 @@
 """Device tensors of the cache and the grouping of cache layers by what they keep.
 
 Keys and values of a group live in one tensor ``[layers, 2, pages, kv_heads, page_tokens,
-head_dim]``: the rows of one (page, head) are contiguous (``page_tokens * head_dim`` elements), so
+head_dim]`` (``[layers, 1, ...]`` for a group that keeps one row per token, which is then both): the rows of one (page, head) are contiguous (``page_tokens * head_dim`` elements), so
 a kernel that walks a request's context for one head reads whole contiguous runs. Fixed-size
 per-request state lives in ``[layers, max_requests, *shape]`` tensors, indexed by state slot.
 
@@ -33,13 +33,14 @@ def group_cache_layers(needs: dict[int, object], page_tokens: int):
                 paged += 1
                 if paged > 1:
                     raise TypeError(f"cache layer {cid}: more than one set of pages")
-                kv.setdefault((need.num_kv_heads, need.head_dim, need.window, need.dtype), []).append(cid)
+                kv.setdefault((need.num_kv_heads, need.head_dim, need.window, need.dtype,
+                               2 if need.values else 1), []).append(cid)
             elif isinstance(need, StateNeed):
                 st.setdefault((tuple(need.shape), need.dtype), []).append(cid)
             else:
                 raise TypeError(f"cache layer {cid}: unknown need {need!r}")
     kv_groups = [
-        KVGroupSpec(tuple(ids), nk, d, w, page_tokens, dt) for (nk, d, w, dt), ids in kv.items()
+        KVGroupSpec(tuple(ids), nk, d, w, page_tokens, dt, planes) for (nk, d, w, dt, planes), ids in kv.items()
     ]
     state_groups = [StateGroupSpec(tuple(ids), shape, dt) for (shape, dt), ids in st.items()]
     return kv_groups, state_groups
@@ -85,7 +86,7 @@ class CachePools:
         self.max_requests = max_requests
         self.kv = [
             torch.zeros(
-                len(g.cache_ids), 2, n + 1, g.num_kv_heads, g.page_tokens, g.head_dim,
+                len(g.cache_ids), g.planes, n + 1, g.num_kv_heads, g.page_tokens, g.head_dim,
                 dtype=g.dtype or dtype, device=device,
             )
             for g, n in zip(self.kv_groups, self.num_pages)
@@ -137,7 +138,7 @@ class CachePools:
             return CacheView(-1, 0, None, None, first, writes, states)
         gi, li = where
         t = self.kv[gi][li]
-        return CacheView(gi, self.kv_groups[gi].page_tokens, t[0], t[1], first, writes, states)
+        return CacheView(gi, self.kv_groups[gi].page_tokens, t[0], t[-1], first, writes, states)
 
     def spare_page(self, group: int) -> int:
         """A page of ``group`` that the manager never hands out."""

@@ -84,6 +84,18 @@ def _register_builtin() -> None:
             checkpoint_layout=gubotar_checkpoint_layout,
         )
     )
+    from ..models.pazivik import pazivik_checkpoint_layout, pazivik_plan
+    from .pazivik import PazivikConfig
+
+    register_architecture(
+        Architecture(
+            name="Pazivik",
+            model_type="pazivik",
+            config_cls=PazivikConfig,
+            plan=pazivik_plan,
+            checkpoint_layout=pazivik_checkpoint_layout,
+        )
+    )
 
 
 _register_builtin()

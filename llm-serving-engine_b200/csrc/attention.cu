@@ -4,8 +4,9 @@
 // For a query at absolute position p of a sequence, with keys j of the same sequence:
 //   s_j = scale * q . k_j   for  max(0, p - window + 1) <= j <= p   (window 0: from 0)
 //   o   = sum_j softmax(s)_j * v_j
-// Optional: a factor per head on the score, a penalty slope_h * (p - j) taken off it, and chunks
-// (only keys with j / chunk == p / chunk are read); see LseAttnArgs.
+// Optional: a factor per head on the score, a penalty slope_h * (p - j) taken off it, chunks
+// (only keys with j / chunk == p / chunk are read), and a sink per head (exp(sink_h) joins the
+// softmax's denominator); see LseAttnArgs.
 // Query head h reads key/value head h / (num_heads / num_kv_heads). Scores, the running maximum,
 // the normaliser and the weighted sum are float32 (src/llmserve/kernels/csrc/
 // paged_attention.cpp:191-243 does the same on the CPU). Keys and values are read from pages
@@ -183,6 +184,7 @@ __global__ void __launch_bounds__(128) prefill_simt_kernel(const LseAttnArgs a, 
   }
   if (row_valid) {
     T* o = (T*)a.out + (size_t)(si.q_start + qi) * a.out_row_stride + (size_t)head * D;
+    if (a.sinks && l > 0.f) l += Exp<T>::f(a.sinks[head] - m);
     const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
     for (int i = 0; i < DPT; ++i) o[sub + 4 * i] = Num<T>::from_float(acc[i] * inv);
@@ -266,7 +268,7 @@ __global__ void __launch_bounds__(MMA_THREADS, (LSE_HEAD_DIM <= 64 ? 2 : 1)) pre
   float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.f, 0.f};
   // With score options the scores are finished (factor, distance penalty) when they are masked,
   // and only the change to base 2 is left to the exponent's multiply-add.
-  const bool options = a.head_scale || a.slopes || a.chunk > 0;
+  const bool options = a.head_scale || a.slopes || a.chunk > 0 || a.sinks;
   const float qk_factor = head_factor(a, head);
   const float slope = a.slopes ? a.slopes[head] : 0.f;
   const float sl2 = (options ? 1.f : a.scale) * 1.4426950408889634f;  // scores in the base-2 domain
@@ -401,6 +403,8 @@ __global__ void __launch_bounds__(MMA_THREADS, (LSE_HEAD_DIM <= 64 ? 2 : 1)) pre
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) {
     if (!valid_r[rr]) continue;
+    // with a sink the scores are finished ones (options), so m_r is in their natural units
+    if (a.sinks && l_r[rr] > 0.f) l_r[rr] += expf(a.sinks[head] - m_r[rr]);
     const float inv = l_r[rr] > 0.f ? 1.f / l_r[rr] : 0.f;
     bf16* dst = (bf16*)a.out +
                 (size_t)(si.q_start + q0 + warp * 16 + g + rr * 8) * a.out_row_stride +
@@ -436,7 +440,8 @@ constexpr int MERGE_SPLITS = 64;  // most context partitions per (sequence, head
 // and instruction order of the key loop.
 template <typename T, int GT>
 __device__ __noinline__ void merge_partitions(const float* __restrict__ parts, int num_splits,
-                                              int heads_here, T* __restrict__ out) {
+                                              int heads_here, T* __restrict__ out,
+                                              const float* __restrict__ sinks = nullptr) {
   // parts: partition 0 of this block's first head; heads are num_splits * (D + 2) floats apart.
   // out: this token's row at the first head.
   __shared__ float sm_w[GT][MERGE_SPLITS], sm_L[GT];
@@ -462,6 +467,7 @@ __device__ __noinline__ void merge_partitions(const float* __restrict__ parts, i
       L += ls[k] * wt;
     }
     L = warp_sum(L);
+    if (sinks && L > 0.f) L += Exp<T>::f(sinks[gq] - M);  // sinks: at this block's first head
     if (lane == 0) sm_L[gq] = L;
   }
   __syncthreads();
@@ -658,6 +664,7 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
     const int h = h0 + gq;
     if (a.num_splits == 1) {
       T* o = (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h * D;
+      if (a.sinks && L > 0.f) L += Exp<T>::f(a.sinks[h] - M);
       o[d] = Num<T>::from_float(L > 0.f ? A / L : 0.f);
     } else {
       float* part = a.scratch + LSE_ATTN_COUNTERS +
@@ -686,7 +693,8 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
   __threadfence();
   merge_partitions<T, GT>(
       a.scratch + LSE_ATTN_COUNTERS + ((size_t)b * a.num_heads + h0) * a.num_splits * (D + 2),
-      a.num_splits, heads_here, (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h0 * D);
+      a.num_splits, heads_here, (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h0 * D,
+      a.sinks ? a.sinks + h0 : nullptr);
 }
 
 #if LSE_HEAD_DIM == 64
@@ -1616,7 +1624,7 @@ template <typename T>
 static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
   const int G = a->num_heads / a->num_kv_heads;
   const int ps = shift_of(a->page_tokens);
-  const bool options = a->head_scale || a->slopes || a->chunk > 0;  // served by the CUDA-core kernel only
+  const bool options = a->head_scale || a->slopes || a->chunk > 0 || a->sinks;  // served by the CUDA-core kernel only
 #if LSE_HEAD_DIM == 64 || LSE_HEAD_DIM == 128
   // On the tensor cores: one block per (partition, key/value head, sequence). Also for a single
   // head per key/value head: seven of the tile's eight columns are idle then, but the kernel
@@ -1754,7 +1762,7 @@ extern "C" int lse_attn_prefill(const LseAttnArgs* a, cudaStream_t stream) {
     prefill_simt_kernel<float><<<grid, 128, 0, stream>>>(*a, ps);
 #if LSE_HEAD_DIM == 64
   } else if (a->force_simt == 0 && a->num_rows > 0 && a->num_pages > 0 && atc::supported(a) &&
-             !(a->head_scale || a->slopes || a->chunk > 0)) {
+             !(a->head_scale || a->slopes || a->chunk > 0 || a->sinks)) {
     // 128-row tiles, like the mma.sync kernel
     return atc::launch_prefill(a, a->num_rows, a->num_pages * a->num_kv_heads * a->page_tokens,
                                a->error_flag, stream);

@@ -59,6 +59,9 @@ struct LseAttnArgs {
   const float* head_scale;  // [num_heads] or null
   const float* slopes;      // [num_heads] or null
   int chunk;
+  //   sinks: the softmax's denominator also holds exp(sinks[h]), a term without key or value
+  //   (not multiplied by scale); it counts once per query whatever the context's partitions are.
+  const float* sinks;       // [num_heads] or null
 };
 
 #define LSE_ATTN_COUNTERS 65536  // words at the start of the scratch: one counter per (sequence, head group)

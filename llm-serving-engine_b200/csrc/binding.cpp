@@ -168,14 +168,14 @@ Tensor rope_kv_write(Tensor& qkv, int64_t nq, int64_t nk, int64_t D, const Tenso
   return q;
 }
 
-void silu_mul(const Tensor& gu, Tensor& out) {
+void silu_mul(const Tensor& gu, Tensor& out, int64_t act) {
   check_cuda(gu, "gu");
   check_cuda(out, "out");
   TORCH_CHECK(gu.dim() == 2 && out.dim() == 2 && gu.size(1) == 2 * out.size(1) &&
                   gu.size(0) == out.size(0),
               "silu_mul: gu must be [T, 2I] and out [T, I]");
   done(lse_silu_mul(gu.data_ptr(), dtype_code(gu, "gu"), out.data_ptr(), dtype_code(out, "out"),
-                    (int)gu.size(0), (int)out.size(1), stream()),
+                    (int)gu.size(0), (int)out.size(1), (int)act, stream()),
        "silu_mul");
 }
 
@@ -312,7 +312,7 @@ void paged_attention(const Tensor& q, Tensor& out, const Tensor& k_pages, const 
                      const Tensor& cu_q, const OptTensor& tiles, int64_t num_tiles,
                      const OptTensor& decode_seqs, int64_t num_decode, int64_t num_splits,
                      const OptTensor& scratch, int64_t force_kernel, const OptTensor& head_scale,
-                     const OptTensor& slopes, int64_t chunk) {
+                     const OptTensor& slopes, int64_t chunk, const OptTensor& sinks) {
   const AttnLib& lib = attn_lib(D);
   TORCH_CHECK(q.is_cuda() && q.dim() == 2 && q.stride(1) == 1 && q.size(1) >= num_heads * D,
               "paged_attention: q must be [T, >= heads*head_dim] with unit column stride");
@@ -369,6 +369,11 @@ void paged_attention(const Tensor& q, Tensor& out, const Tensor& k_pages, const 
   }
   TORCH_CHECK(chunk >= 0, "paged_attention: chunk must not be negative");
   a.chunk = (int)chunk;
+  if (sinks) {
+    check_f32(*sinks, "sinks");
+    TORCH_CHECK(sinks->numel() == num_heads, "paged_attention: sinks needs one value per head");
+    a.sinks = sinks->data_ptr<float>();
+  }
   if (num_tiles > 0) {
     TORCH_CHECK(tiles.has_value(), "paged_attention: num_tiles > 0 without tiles");
     check_i32(*tiles, "tiles");
@@ -401,6 +406,168 @@ int out_code(const Tensor& t, const char* what) {
   const int c = dtype_code(t, what);
   TORCH_CHECK(c == LSE_F32 || c == LSE_BF16, what, ": dtype must be float32 or bfloat16");
   return c;
+}
+
+// ------------------------------------------------------------------ embeddings, latent attention, experts
+void hashed_pair_add(Tensor& x, const Tensor& table, Tensor& state, const Tensor& ids,
+                     const Tensor& positions, const Tensor& token_seq, const Tensor& cu_q,
+                     const Tensor& slots, int64_t buckets, int64_t mul_prev, int64_t mul_cur) {
+  check_f32(x, "x");
+  check_cuda(table, "table");
+  check_i32(ids, "ids");
+  check_i32(positions, "positions");
+  check_i32(token_seq, "token_seq");
+  check_i32(cu_q, "cu_q");
+  check_i32(slots, "slots");
+  TORCH_CHECK(state.is_cuda() && state.is_contiguous() && state.scalar_type() == torch::kInt32,
+              "hashed_pair_add: state must be a contiguous int32 CUDA tensor");
+  const int T = (int)x.size(0), W = (int)x.size(1);
+  TORCH_CHECK(x.dim() == 2 && table.dim() == 2 && table.size(1) == W && table.size(0) == buckets + 1,
+              "hashed_pair_add: table must be [buckets + 1, width]");
+  TORCH_CHECK(ids.numel() == T && positions.numel() == T && token_seq.numel() == T &&
+                  cu_q.numel() == slots.numel() + 1 && state.numel() >= 1,
+              "hashed_pair_add: lengths differ");
+  TORCH_CHECK(buckets > 0 && mul_prev >= 0 && mul_cur >= 0, "hashed_pair_add: bad constants");
+  done(lse_hashed_pair_add(x.data_ptr<float>(), table.data_ptr(), out_code(table, "table"),
+                           state.data_ptr<int>(), ids.data_ptr<int>(), positions.data_ptr<int>(),
+                           token_seq.data_ptr<int>(), cu_q.data_ptr<int>(), slots.data_ptr<int>(), T, W,
+                           (long long)buckets, (long long)mul_prev, (long long)mul_cur, stream()),
+       "hashed_pair_add");
+}
+
+void sinusoid_add(Tensor& x, const Tensor& positions, const Tensor& freq) {
+  check_f32(x, "x");
+  check_i32(positions, "positions");
+  check_f32(freq, "freq");
+  TORCH_CHECK(x.dim() == 2 && positions.numel() == x.size(0) && freq.numel() * 2 >= x.size(1),
+              "sinusoid_add: need x [T, W], positions [T] and freq [ceil(W / 2)]");
+  done(lse_sinusoid_add(x.data_ptr<float>(), positions.data_ptr<int>(), freq.data_ptr<float>(),
+                        (int)x.size(0), (int)x.size(1), stream()),
+       "sinusoid_add");
+}
+
+void latent_write(const Tensor& proj, int64_t col0, int64_t R, const Tensor& weight, double eps,
+                  Tensor& pages, const Tensor& positions, const Tensor& token_seq,
+                  const Tensor& block_tables) {
+  check_cuda(proj, "proj");
+  check_f32(weight, "weight");
+  check_cuda(pages, "pages");
+  check_i32(positions, "positions");
+  check_i32(token_seq, "token_seq");
+  check_i32(block_tables, "block_tables");
+  TORCH_CHECK(proj.dim() == 2 && col0 >= 0 && R > 0 && col0 + R <= proj.size(1), "latent_write: columns outside proj");
+  TORCH_CHECK(pages.dim() == 4 && pages.size(1) == 1 && pages.size(3) >= R,
+              "latent_write: pages must be [pages, 1, page_tokens, >= rank]");
+  TORCH_CHECK(weight.numel() == R, "latent_write: one weight per latent dim");
+  const int T = (int)proj.size(0);
+  TORCH_CHECK(positions.numel() == T && token_seq.numel() == T && block_tables.dim() == 2,
+              "latent_write: lengths differ");
+  done(lse_latent_write(proj.data_ptr(), out_code(proj, "proj"), proj.size(1), (int)col0, (int)R,
+                        (int)pages.size(3), weight.data_ptr<float>(), (float)eps, pages.data_ptr(),
+                        out_code(pages, "pages"), positions.data_ptr<int>(), token_seq.data_ptr<int>(),
+                        block_tables.data_ptr<int>(), (int)block_tables.size(1), (int)pages.size(2), T,
+                        stream()),
+       "latent_write");
+}
+
+// out[t, h, :] = w[h] . a[t, col0 + h*K : col0 + (h+1)*K]     w [H, N, K], out [T, H*N]
+void head_linear(const Tensor& a, int64_t col0, const Tensor& w, Tensor& out) {
+  check_cuda(a, "a");
+  check_cuda(w, "w");
+  check_cuda(out, "out");
+  TORCH_CHECK(a.dim() == 2 && w.dim() == 3 && out.dim() == 2, "head_linear: need a [T, >= H*K], w [H, N, K], out [T, H*N]");
+  const int64_t H = w.size(0), N = w.size(1), K = w.size(2);
+  TORCH_CHECK(col0 >= 0 && col0 + H * K <= a.size(1) && out.size(0) == a.size(0) && out.size(1) == H * N,
+              "head_linear: shapes disagree");
+  done(lse_head_linear(a.data_ptr(), out_code(a, "a"), a.size(1), col0, w.data_ptr(), out_code(w, "w"),
+                       out.data_ptr(), out_code(out, "out"), (int)a.size(0), (int)H, (int)N, (int)K, stream()),
+       "head_linear");
+}
+
+void moe_route(const Tensor& h, const Tensor& router, int64_t E, int64_t top, Tensor& idx, Tensor& wts,
+               const OptTensor& gate) {
+  check_cuda(h, "h");
+  check_f32(router, "router");
+  check_i32(idx, "idx");
+  check_f32(wts, "wts");
+  const int64_t T = h.size(0), W = h.size(1);
+  const int has_gate = gate.has_value() ? 1 : 0;
+  TORCH_CHECK(h.dim() == 2 && router.dim() == 2 && router.size(1) == W && router.size(0) == E + has_gate,
+              "moe_route: router must be [experts (+1 with a gate), width]");
+  TORCH_CHECK(idx.numel() == T * top && wts.numel() == T * top, "moe_route: idx and wts must be [T, top]");
+  float* g = nullptr;
+  if (gate) {
+    check_f32(*gate, "gate");
+    TORCH_CHECK(gate->numel() == T, "moe_route: gate must be [T]");
+    g = gate->data_ptr<float>();
+  }
+  done(lse_moe_route(h.data_ptr(), out_code(h, "h"), router.data_ptr<float>(), (int)T, (int)W, (int)E,
+                     has_gate, (int)top, idx.data_ptr<int>(), wts.data_ptr<float>(), g, stream()),
+       "moe_route");
+}
+
+// work: int32 [>= (E + 1) + 2 n + 2 max_tiles + 1] holding offsets | perm | pos_of | tile_batch |
+// tile_row0 | num_tiles, max_tiles = n / tile_rows + E.
+int64_t moe_max_tiles(int64_t n, int64_t E) { return n / lse_moe_tile_rows() + E; }
+
+void moe_sort(const Tensor& idx, int64_t E, Tensor& work) {
+  check_i32(idx, "idx");
+  check_i32(work, "work");
+  const int64_t n = idx.numel(), mt = moe_max_tiles(n, E);
+  TORCH_CHECK(work.numel() >= E + 1 + 2 * n + 2 * mt + 1, "moe_sort: work too small");
+  int* p = work.data_ptr<int>();
+  done(lse_moe_sort(idx.data_ptr<int>(), (int)n, (int)E, p, p + E + 1, p + E + 1 + n, p + E + 1 + 2 * n,
+                    p + E + 1 + 2 * n + mt, p + E + 1 + 2 * n + 2 * mt, stream()),
+       "moe_sort");
+}
+
+// out[r] = w[expert of sorted row r] . a-row(r); gather: a-row(r) = a[choice / top] * wts[choice]
+void expert_linear(const Tensor& a, const Tensor& w, Tensor& out, const Tensor& work, int64_t n, int64_t top,
+                   const OptTensor& wts) {
+  check_cuda(a, "a");
+  check_cuda(w, "w");
+  check_f32(out, "out");
+  check_i32(work, "work");
+  TORCH_CHECK(a.dim() == 2 && w.dim() == 3 && out.dim() == 2 && w.size(2) == a.size(1) && out.size(0) == n &&
+                  out.size(1) == w.size(1),
+              "expert_linear: need a [rows, K], w [E, N, K], out [n, N]");
+  const int64_t E = w.size(0), mt = moe_max_tiles(n, E);
+  TORCH_CHECK(work.numel() >= E + 1 + 2 * n + 2 * mt + 1, "expert_linear: work too small");
+  const bool gather = top > 0;
+  TORCH_CHECK(gather ? a.size(0) * top == n : a.size(0) == n, "expert_linear: rows of a disagree with n");
+  const float* sc = nullptr;
+  if (wts) {
+    check_f32(*wts, "wts");
+    TORCH_CHECK(gather && wts->numel() == n, "expert_linear: wts must be [n] and needs top");
+    sc = wts->data_ptr<float>();
+  }
+  const int* p = work.data_ptr<int>();
+  done(lse_expert_linear(a.data_ptr(), out_code(a, "a"), a.size(1), gather ? p + E + 1 : nullptr,
+                         gather ? (int)top : 1, sc, w.data_ptr(), out_code(w, "w"), out.data_ptr<float>(),
+                         (int)n, (int)w.size(1), (int)w.size(2), p, p + E + 1 + 2 * n, p + E + 1 + 2 * n + mt,
+                         p + E + 1 + 2 * n + 2 * mt, (int)mt, stream()),
+       "expert_linear");
+}
+
+void moe_combine(const Tensor& y, const Tensor& work, int64_t E, int64_t top, const OptTensor& shared_out,
+                 const OptTensor& gate, Tensor& out, bool accumulate) {
+  check_f32(y, "y");
+  check_i32(work, "work");
+  check_f32(out, "out");
+  const int64_t n = y.size(0), T = out.size(0), W = out.size(1);
+  TORCH_CHECK(y.dim() == 2 && out.dim() == 2 && y.size(1) == W && n == T * top, "moe_combine: shapes disagree");
+  const float *sp = nullptr, *gp = nullptr;
+  if (shared_out) {
+    check_f32(*shared_out, "shared_out");
+    TORCH_CHECK(gate.has_value() && shared_out->sizes() == out.sizes(), "moe_combine: shared_out needs a gate and out's shape");
+    check_f32(*gate, "gate");
+    TORCH_CHECK(gate->numel() == T, "moe_combine: gate must be [T]");
+    sp = shared_out->data_ptr<float>();
+    gp = gate->data_ptr<float>();
+  }
+  done(lse_moe_combine(y.data_ptr<float>(), work.data_ptr<int>() + E + 1 + n, (int)top, sp, gp,
+                       out.data_ptr<float>(), accumulate ? 1 : 0, (int)T, (int)W, stream()),
+       "moe_combine");
 }
 
 void cast_f32(const Tensor& x, Tensor& out) {
@@ -787,7 +954,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding", &embedding);
   m.def("add_rmsnorm", &add_rmsnorm);
   m.def("rope_kv_write", &rope_kv_write);
-  m.def("silu_mul", &silu_mul);
+  m.def("silu_mul", &silu_mul, py::arg("gu"), py::arg("out"), py::arg("act") = 0);
   m.def("gemm_f32", &gemm_f32);
   m.def("gemm_bf16_skinny", &gemm_bf16_skinny);
   m.def("gemm_bf16_skinny_max_rows", &gemm_bf16_skinny_max_rows);
@@ -798,7 +965,21 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attention_q_tile", &attention_q_tile);
   m.def("attention_scratch_floats", &attention_scratch_floats);
   m.def("attention_decode_blocks_per_sm", &attention_decode_blocks_per_sm);
-  m.def("paged_attention", &paged_attention);
+  m.def("paged_attention", &paged_attention, py::arg("q"), py::arg("out"), py::arg("k_pages"), py::arg("v_pages"),
+        py::arg("num_heads"), py::arg("num_kv_heads"), py::arg("head_dim"), py::arg("scale"), py::arg("window"),
+        py::arg("block_tables"), py::arg("ctx_lens"), py::arg("cu_q"), py::arg("tiles"), py::arg("num_tiles"),
+        py::arg("decode_seqs"), py::arg("num_decode"), py::arg("num_splits"), py::arg("scratch"),
+        py::arg("force_kernel"), py::arg("head_scale"), py::arg("slopes"), py::arg("chunk"),
+        py::arg("sinks") = py::none());
+  m.def("hashed_pair_add", &hashed_pair_add);
+  m.def("sinusoid_add", &sinusoid_add);
+  m.def("latent_write", &latent_write);
+  m.def("head_linear", &head_linear);
+  m.def("moe_route", &moe_route);
+  m.def("moe_max_tiles", &moe_max_tiles);
+  m.def("moe_sort", &moe_sort);
+  m.def("expert_linear", &expert_linear);
+  m.def("moe_combine", &moe_combine);
   m.def("cast_f32", &cast_f32);
   m.def("token_shift", &token_shift);
   m.def("rmsnorm_add", &rmsnorm_add);

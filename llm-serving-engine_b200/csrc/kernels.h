@@ -44,10 +44,12 @@ int lse_rope_kv_write(const void* qkv, int in_dtype, void* q_out, int dtype, int
                       const float* sin, void* k_pages, void* v_pages, const int* block_tables,
                       int table_stride, int page_tokens, cudaStream_t stream);
 
-// out[t, i] = silu(gu[t, i]) * gu[t, I + i]     gu [T, 2I] of in_dtype, out [T, I] of dtype
+// out[t, i] = act(gu[t, i]) * gu[t, I + i]     gu [T, 2I] of in_dtype, out [T, I] of dtype
 // (in_dtype == dtype, or float32 / LSE_FIXED64 in and bfloat16 out; a fixed-point input is cleared
-// as it is read).
-int lse_silu_mul(const void* gu, int in_dtype, void* out, int dtype, int T, int I,
+// as it is read). act: LSE_ACT_SILU (a / (1 + exp(-a))) or LSE_ACT_GELU_TANH (the tanh form of gelu).
+#define LSE_ACT_SILU 0
+#define LSE_ACT_GELU_TANH 1
+int lse_silu_mul(const void* gu, int in_dtype, void* out, int dtype, int T, int I, int act,
                  cudaStream_t stream);
 
 // True float32 matrix product: out[T, N] = a[T, K] . w[N, K]^T (+ bias[N]). Each output element is
@@ -164,4 +166,55 @@ int lse_decay_linear_attention(const float* proj, long long stride, float* out, 
                                const int* slots, int num_seqs, int H, int dk, int dv,
                                const float* cos, const float* sin, int rot, int silu,
                                float key_scale, int max_chunks, float* chunks, cudaStream_t stream);
+// ---- table-sum embeddings, latent attention, routed experts (latent_moe.cu)
+
+// x[t] += table[row], row = (previous token * mul_prev + token * mul_cur) mod buckets, or row
+// `buckets` (the table's last) at position 0. The previous token of a sequence's first row of the
+// step is state[slots[seq]] (int32, one per slot); afterwards the state holds the sequence's last
+// token of the step.   x float32 [T, W], table [buckets + 1, W]
+int lse_hashed_pair_add(float* x, const void* table, int table_dtype, int* state, const int* ids,
+                        const int* positions, const int* token_seq, const int* cu_q,
+                        const int* slots, int T, int W, long long buckets, long long mul_prev,
+                        long long mul_cur, cudaStream_t stream);
+
+// x[t, i] += sin(p * freq[i / 2]) for even i, cos(...) for odd i; p = float(positions[t])
+int lse_sinusoid_add(float* x, const int* positions, const float* freq, int T, int W,
+                     cudaStream_t stream);
+
+// Row t of proj (columns col0 .. col0 + R - 1, row stride `stride`) divided by its root mean
+// square (eps inside the root), times weight[R], written as `dtype` into the token's place of
+// pages [pages, 1, page_tokens, Rp]; columns R .. Rp - 1 are written as zeros.
+int lse_latent_write(const void* proj, int in_dtype, long long stride, int col0, int R, int Rp,
+                     const float* weight, float eps, void* pages, int dtype, const int* positions,
+                     const int* token_seq, const int* block_tables, int table_stride,
+                     int page_tokens, int T, cudaStream_t stream);
+
+// A product per head: out[t, h*N + n] = sum_k a[t*a_stride + a_col0 + h*K + k] * w[(h*N + n)*K + k]
+// with float32 accumulation in ascending k by one thread (a row's result does not depend on T).
+// Served: (a, w, out) = (f32, f32, f32), (f32 | bf16, bf16, bf16 | f32).
+int lse_head_linear(const void* a, int a_dtype, long long a_stride, long long a_col0, const void* w,
+                    int w_dtype, void* out, int out_dtype, int T, int H, int N, int K,
+                    cudaStream_t stream);
+
+// Routed experts. h [T, W]; router float32 [E (+1), W].
+//   lse_moe_route: scores = sigmoid(router . h); idx/wts [T, top] the top experts (largest score
+//     first, the lower index on a tie) and their scores; with has_gate, gate[t] = sigmoid(router[E] . h).
+//   lse_moe_sort: the n = T * top choices sorted by expert: offsets [E + 1], perm [n] (sorted row ->
+//     choice), pos_of [n] (choice -> sorted row), and tiles of at most lse_moe_tile_rows() rows of one
+//     expert each (tile_batch, tile_row0: room for n / tile_rows + E entries; num_tiles [1]).
+//   lse_expert_linear: out[r, :] = w[expert of r] . arow(r) for every sorted row r, float32 out
+//     [rows, N]; arow(r) = a[a_rows[r] / a_div] * a_scale[a_rows[r]] (a_rows null: a[r], unscaled);
+//     w [E, N, K]. Launched for max_tiles tiles; tiles beyond *num_tiles do nothing.
+//   lse_moe_combine: out[t] (+)= sum_k y[pos_of[t*top + k]] (+ gate[t] * shared_out[t]).
+int lse_moe_tile_rows(void);
+int lse_moe_route(const void* h, int h_dtype, const float* router, int T, int W, int E, int has_gate,
+                  int top, int* idx, float* wts, float* gate, cudaStream_t stream);
+int lse_moe_sort(const int* idx, int n, int E, int* offsets, int* perm, int* pos_of, int* tile_batch,
+                 int* tile_row0, int* num_tiles, cudaStream_t stream);
+int lse_expert_linear(const void* a, int a_dtype, long long a_stride, const int* a_rows, int a_div,
+                      const float* a_scale, const void* w, int w_dtype, float* out, int rows, int N,
+                      int K, const int* offsets, const int* tile_batch, const int* tile_row0,
+                      const int* num_tiles, int max_tiles, cudaStream_t stream);
+int lse_moe_combine(const float* y, const int* pos_of, int top, const float* shared_out,
+                    const float* gate, float* out, int accumulate, int T, int W, cudaStream_t stream);
 }

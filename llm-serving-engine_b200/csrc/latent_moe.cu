@@ -1,0 +1,435 @@
+// Kernels of latent attention, routed experts and table-sum embeddings.
+//
+//   hashed_pair_add   x[t] += table[row(previous token, token)], the previous token kept per request
+//   sinusoid_add      x[t, 2i] += sin(p f_i), x[t, 2i+1] += cos(p f_i)
+//   latent_write      RMS norm of a projected latent row, written into the token's page
+//   rows_gemm         float32-accumulating products on the CUDA cores whose rows may be gathered
+//                     and scaled and whose weights are chosen per head (batched over heads) or per
+//                     tile (experts); each output element is one thread's in-order sum over k, so
+//                     a row's result does not depend on the batch it is in
+//   moe_route         sigmoid scores of a router, the top-k experts per token, a shared gate
+//   moe_sort          tokens' expert choices sorted by expert, as tiles of rows for rows_gemm
+//   moe_combine       per token: the sum of its experts' rows (+ gate * shared expert), into x
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lse {
+
+// ------------------------------------------------------------------------------------ embeddings
+template <typename T>
+__global__ void __launch_bounds__(128)
+hashed_pair_add_kernel(float* __restrict__ x, const T* __restrict__ table, int* __restrict__ state,
+                       const int* __restrict__ ids, const int* __restrict__ positions,
+                       const int* __restrict__ token_seq, const int* __restrict__ cu_q,
+                       const int* __restrict__ slots, int W, long long buckets, long long mul_prev,
+                       long long mul_cur) {
+  const int t = blockIdx.x;
+  const int seq = token_seq[t];
+  const int first = cu_q[seq];
+  const int cur = ids[t];
+  long long row = buckets;  // a sequence's first token
+  if (positions[t] > 0) {
+    const int prev = (t == first) ? state[slots[seq]] : ids[t - 1];
+    row = ((long long)prev * mul_prev + (long long)cur * mul_cur) % buckets;
+  }
+  __syncthreads();  // the state was read before it is written below
+  // the block of a sequence's first row is the only one that touches the sequence's state
+  if (t == first && threadIdx.x == 0) state[slots[seq]] = ids[cu_q[seq + 1] - 1];
+  const T* src = table + (size_t)row * W;
+  float* dst = x + (size_t)t * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) dst[i] += Num<T>::to_float(src[i]);
+}
+
+__global__ void __launch_bounds__(128)
+sinusoid_add_kernel(float* __restrict__ x, const int* __restrict__ positions,
+                    const float* __restrict__ freq, int W) {
+  const int t = blockIdx.x;
+  const float p = (float)positions[t];
+  float* dst = x + (size_t)t * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float ang = p * freq[i >> 1];  // the angle is a float32 product, as positions are float32
+    dst[i] += (i & 1) ? cosf(ang) : sinf(ang);
+  }
+}
+
+// ------------------------------------------------------------------------------------ latent rows
+template <typename TIn, typename T>
+__global__ void __launch_bounds__(128)
+latent_write_kernel(const TIn* __restrict__ proj, long long stride, int col0, int R, int Rp,
+                    const float* __restrict__ weight, float eps, T* __restrict__ pages,
+                    const int* __restrict__ positions, const int* __restrict__ token_seq,
+                    const int* __restrict__ block_tables, int table_stride, int page_tokens) {
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const TIn* src = proj + (size_t)t * stride + col0;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < R; i += blockDim.x) {
+    const float v = Num<TIn>::to_float(src[i]);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float r = rsqrtf(ss / (float)R + eps);
+  const int pos = positions[t];
+  const int page = block_tables[(size_t)token_seq[t] * table_stride + pos / page_tokens];
+  T* dst = pages + ((size_t)page * page_tokens + pos % page_tokens) * Rp;
+  for (int i = threadIdx.x; i < Rp; i += blockDim.x)
+    dst[i] = Num<T>::from_float(i < R ? Num<TIn>::to_float(src[i]) * r * weight[i] : 0.f);
+}
+
+// ------------------------------------------------------------------------------------ rows_gemm
+constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;  // 256 threads, 4x4 outputs each
+
+struct RowsGemm {
+  const void* a;            // [rows, a_stride] (+ a_col0 + batch * a_batch_cols)
+  long long a_stride;
+  long long a_col0, a_batch_cols;
+  const int* a_rows;        // null, or logical row r reads row a_rows[r] / a_div ...
+  int a_div;
+  const float* a_scale;     // ... multiplied by a_scale[a_rows[r]] (null: not scaled)
+  const void* w;            // [N, K] at w + batch * w_batch_stride
+  long long w_batch_stride;
+  void* out;                // [rows, out_stride] (+ batch * out_batch_cols)
+  long long out_stride, out_batch_cols;
+  // tiles of rows that belong to one batch entry each (null: all rows, batch = blockIdx.z)
+  const int* tile_batch;
+  const int* tile_row0;
+  const int* offsets;       // [batches + 1] row ranges of the batch entries
+  const int* num_tiles;
+  int T, N, K;
+};
+
+template <typename TA, typename TW, typename TO>
+__global__ void __launch_bounds__(256) rows_gemm_kernel(const RowsGemm g) {
+  __shared__ float as[BK][BM + 4];
+  __shared__ float ws[BK][BN + 4];
+  __shared__ int srow[BM];
+  __shared__ float sscale[BM];
+  const int tid = threadIdx.x;
+  int batch, m0, m_end;
+  if (g.tile_batch) {
+    if ((int)blockIdx.y >= *g.num_tiles) return;
+    batch = g.tile_batch[blockIdx.y];
+    m0 = g.tile_row0[blockIdx.y];
+    m_end = min(g.offsets[batch + 1], m0 + BM);
+  } else {
+    batch = blockIdx.z;
+    m0 = blockIdx.y * BM;
+    m_end = min(g.T, m0 + BM);
+  }
+  if (tid < BM) {
+    const int r = m0 + tid;
+    int row = -1;
+    float sc = 1.f;
+    if (r < m_end) {
+      const int idx = g.a_rows ? g.a_rows[r] : r;
+      row = g.a_rows ? idx / g.a_div : r;
+      if (g.a_scale) sc = g.a_scale[idx];
+    }
+    srow[tid] = row;
+    sscale[tid] = sc;
+  }
+  __syncthreads();
+  const int N = g.N, K = g.K;
+  const int n0 = blockIdx.x * BN;
+  const TA* a = (const TA*)g.a + g.a_col0 + (long long)batch * g.a_batch_cols;
+  const TW* w = (const TW*)g.w + (long long)batch * g.w_batch_stride;
+  const int tm = (tid / 16) * TM, tn = (tid % 16) * TN;
+  float acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+  const int lr = tid / 4, lk = (tid % 4) * 4;
+  const int arow = srow[lr];
+  const float asc = sscale[lr];
+  const int gn = n0 + lr;
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    float av[4] = {0.f, 0.f, 0.f, 0.f}, wv[4] = {0.f, 0.f, 0.f, 0.f};
+    const int gk = k0 + lk;
+    if (arow >= 0) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (gk + j < K) av[j] = Num<TA>::to_float(a[(size_t)arow * g.a_stride + gk + j]) * asc;
+    }
+    if (gn < N) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (gk + j < K) wv[j] = Num<TW>::to_float(w[(size_t)gn * K + gk + j]);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      as[lk + j][lr] = av[j];
+      ws[lk + j][lr] = wv[j];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float ar[TM], wr[TN];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) ar[i] = as[kk][tm + i];
+#pragma unroll
+      for (int j = 0; j < TN; ++j) wr[j] = ws[kk][tn + j];
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(ar[i], wr[j], acc[i][j]);
+    }
+  }
+  TO* out = (TO*)g.out + (long long)batch * g.out_batch_cols;
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int r = m0 + tm + i;
+    if (r >= m_end) continue;
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      const int n = n0 + tn + j;
+      if (n < N) out[(size_t)r * g.out_stride + n] = Num<TO>::from_float(acc[i][j]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------ routing
+// One warp per token. scores = sigmoid(router . h) in float32; the `top` largest (the lower index
+// on a tie) with their scores; row E of the router, if there is one, is the shared expert's gate.
+constexpr int ROUTE_WARPS = 4;
+
+template <typename TH>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ router, int T, int W, int E,
+                 int has_gate, int top, int* __restrict__ idx, float* __restrict__ wts,
+                 float* __restrict__ gate) {
+  extern __shared__ float sm_scores[];  // [ROUTE_WARPS][E]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  if (t >= T) return;
+  float* s = sm_scores + warp * E;
+  const TH* row = h + (size_t)t * W;
+  for (int e = 0; e < E + has_gate; ++e) {
+    const float* r = router + (size_t)e * W;
+    float d = 0.f;
+    for (int i = lane; i < W; i += 32) d = fmaf(Num<TH>::to_float(row[i]), r[i], d);
+    d = warp_sum(d);
+    const float sg = 1.f / (1.f + expf(-d));
+    if (lane == 0) {
+      if (e < E) s[e] = sg;
+      else gate[t] = sg;
+    }
+  }
+  __syncwarp();
+  for (int k = 0; k < top; ++k) {
+    float best = -2.f;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32)
+      if (s[e] > best) {
+        best = s[e];
+        bi = e;
+      }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) {
+        best = ob;
+        bi = oi;
+      }
+    }
+    if (lane == 0) {
+      idx[(size_t)t * top + k] = bi;
+      wts[(size_t)t * top + k] = best;
+      s[bi] = -1.f;  // taken (a sigmoid is never negative)
+    }
+    __syncwarp();
+  }
+}
+
+// One block. n choices idx[i] in [0, E): offsets[e] .. offsets[e+1] are expert e's rows in the
+// sorted order, perm[r] the choice at sorted row r, pos_of[i] the sorted row of choice i, and the
+// rows as tiles of at most BM rows of one expert (tile_batch, tile_row0, num_tiles).
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* __restrict__ idx, int n, int E, int* __restrict__ offsets,
+                int* __restrict__ perm, int* __restrict__ pos_of, int* __restrict__ tile_batch,
+                int* __restrict__ tile_row0, int* __restrict__ num_tiles) {
+  extern __shared__ int sm_sort[];  // counts[E], start[E + 1], tile_start[E + 1]
+  int* counts = sm_sort;
+  int* start = counts + E;
+  int* tstart = start + E + 1;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&counts[idx[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      start[e] = run;
+      tstart[e] = tiles;
+      run += counts[e];
+      tiles += (counts[e] + BM - 1) / BM;
+    }
+    start[E] = run;
+    tstart[E] = tiles;
+    *num_tiles = tiles;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = start[e];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int nt = tstart[e + 1] - tstart[e];
+    for (int k = 0; k < nt; ++k) {
+      tile_batch[tstart[e] + k] = e;
+      tile_row0[tstart[e] + k] = start[e] + k * BM;
+    }
+    counts[e] = 0;  // now the cursor of expert e
+  }
+  __syncthreads();
+  // the order of an expert's rows among themselves is free: every row's result stands alone
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = idx[i];
+    const int r = start[e] + atomicAdd(&counts[e], 1);
+    perm[r] = i;
+    pos_of[i] = r;
+  }
+}
+
+// x[t] (or out[t]) (+)= sum_k y[pos_of[t * top + k]] + gate[t] * shared[t]
+__global__ void __launch_bounds__(128)
+moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of, int top,
+                   const float* __restrict__ shared_out, const float* __restrict__ gate,
+                   float* __restrict__ out, int accumulate, int W) {
+  const int t = blockIdx.x;
+  const float g = gate ? gate[t] : 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float v = 0.f;
+    for (int k = 0; k < top; ++k) v += y[(size_t)pos_of[(size_t)t * top + k] * W + i];
+    if (shared_out) v += g * shared_out[(size_t)t * W + i];
+    float* o = out + (size_t)t * W + i;
+    *o = accumulate ? *o + v : v;
+  }
+}
+
+}  // namespace lse
+
+using namespace lse;
+
+#define LSE_CHECK_LAUNCH() (cudaPeekAtLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED)
+
+extern "C" int lse_hashed_pair_add(float* x, const void* table, int table_dtype, int* state,
+                                   const int* ids, const int* positions, const int* token_seq,
+                                   const int* cu_q, const int* slots, int T, int W, long long buckets,
+                                   long long mul_prev, long long mul_cur, cudaStream_t stream) {
+  if (T <= 0) return LSE_OK;
+  if (buckets <= 0 || W <= 0) return LSE_BAD_ARGUMENT;
+  if (table_dtype == LSE_F32)
+    hashed_pair_add_kernel<float><<<T, 128, 0, stream>>>(x, (const float*)table, state, ids, positions, token_seq,
+                                                         cu_q, slots, W, buckets, mul_prev, mul_cur);
+  else if (table_dtype == LSE_BF16)
+    hashed_pair_add_kernel<bf16><<<T, 128, 0, stream>>>(x, (const bf16*)table, state, ids, positions, token_seq,
+                                                        cu_q, slots, W, buckets, mul_prev, mul_cur);
+  else
+    return LSE_BAD_ARGUMENT;
+  return LSE_CHECK_LAUNCH();
+}
+
+extern "C" int lse_sinusoid_add(float* x, const int* positions, const float* freq, int T, int W,
+                                cudaStream_t stream) {
+  if (T <= 0) return LSE_OK;
+  sinusoid_add_kernel<<<T, 128, 0, stream>>>(x, positions, freq, W);
+  return LSE_CHECK_LAUNCH();
+}
+
+extern "C" int lse_latent_write(const void* proj, int in_dtype, long long stride, int col0, int R,
+                                int Rp, const float* weight, float eps, void* pages, int dtype,
+                                const int* positions, const int* token_seq, const int* block_tables,
+                                int table_stride, int page_tokens, int T, cudaStream_t stream) {
+  if (T <= 0) return LSE_OK;
+  if (R <= 0 || Rp < R || page_tokens <= 0) return LSE_BAD_ARGUMENT;
+#define LSE_LATENT(TIn, T_) \
+  latent_write_kernel<TIn, T_><<<T, 128, 0, stream>>>((const TIn*)proj, stride, col0, R, Rp, weight, eps, \
+      (T_*)pages, positions, token_seq, block_tables, table_stride, page_tokens)
+  if (in_dtype == LSE_F32 && dtype == LSE_F32) LSE_LATENT(float, float);
+  else if (in_dtype == LSE_F32 && dtype == LSE_BF16) LSE_LATENT(float, bf16);
+  else if (in_dtype == LSE_BF16 && dtype == LSE_BF16) LSE_LATENT(bf16, bf16);
+  else return LSE_BAD_ARGUMENT;
+#undef LSE_LATENT
+  return LSE_CHECK_LAUNCH();
+}
+
+static int launch_rows_gemm(const RowsGemm& g, int a_dtype, int w_dtype, int out_dtype, dim3 grid,
+                            cudaStream_t stream) {
+  if (grid.y > 65535 || grid.z > 65535) return LSE_BAD_ARGUMENT;
+#define LSE_RG(TA, TW, TO) rows_gemm_kernel<TA, TW, TO><<<grid, 256, 0, stream>>>(g)
+  if (a_dtype == LSE_F32 && w_dtype == LSE_F32 && out_dtype == LSE_F32) LSE_RG(float, float, float);
+  else if (a_dtype == LSE_F32 && w_dtype == LSE_BF16 && out_dtype == LSE_BF16) LSE_RG(float, bf16, bf16);
+  else if (a_dtype == LSE_F32 && w_dtype == LSE_BF16 && out_dtype == LSE_F32) LSE_RG(float, bf16, float);
+  else if (a_dtype == LSE_BF16 && w_dtype == LSE_BF16 && out_dtype == LSE_BF16) LSE_RG(bf16, bf16, bf16);
+  else if (a_dtype == LSE_BF16 && w_dtype == LSE_BF16 && out_dtype == LSE_F32) LSE_RG(bf16, bf16, float);
+  else return LSE_BAD_ARGUMENT;
+#undef LSE_RG
+  return LSE_CHECK_LAUNCH();
+}
+
+extern "C" int lse_head_linear(const void* a, int a_dtype, long long a_stride, long long a_col0,
+                               const void* w, int w_dtype, void* out, int out_dtype, int T, int H,
+                               int N, int K, cudaStream_t stream) {
+  if (T <= 0 || H <= 0 || N <= 0) return LSE_OK;
+  if (K <= 0) return LSE_BAD_ARGUMENT;
+  RowsGemm g = {};
+  g.a = a; g.a_stride = a_stride; g.a_col0 = a_col0; g.a_batch_cols = K; g.a_div = 1;
+  g.w = w; g.w_batch_stride = (long long)N * K;
+  g.out = out; g.out_stride = (long long)H * N; g.out_batch_cols = N;
+  g.T = T; g.N = N; g.K = K;
+  return launch_rows_gemm(g, a_dtype, w_dtype, out_dtype, dim3((N + BN - 1) / BN, (T + BM - 1) / BM, H), stream);
+}
+
+extern "C" int lse_moe_tile_rows(void) { return BM; }
+
+extern "C" int lse_expert_linear(const void* a, int a_dtype, long long a_stride, const int* a_rows,
+                                 int a_div, const float* a_scale, const void* w, int w_dtype,
+                                 float* out, int rows, int N, int K, const int* offsets,
+                                 const int* tile_batch, const int* tile_row0, const int* num_tiles,
+                                 int max_tiles, cudaStream_t stream) {
+  if (rows <= 0 || N <= 0 || max_tiles <= 0) return LSE_OK;
+  if (K <= 0 || a_div <= 0 || !offsets || !tile_batch || !tile_row0 || !num_tiles) return LSE_BAD_ARGUMENT;
+  RowsGemm g = {};
+  g.a = a; g.a_stride = a_stride; g.a_rows = a_rows; g.a_div = a_div; g.a_scale = a_scale;
+  g.w = w; g.w_batch_stride = (long long)N * K;
+  g.out = out; g.out_stride = N;
+  g.tile_batch = tile_batch; g.tile_row0 = tile_row0; g.offsets = offsets; g.num_tiles = num_tiles;
+  g.T = rows; g.N = N; g.K = K;
+  return launch_rows_gemm(g, a_dtype, w_dtype, LSE_F32, dim3((N + BN - 1) / BN, max_tiles, 1), stream);
+}
+
+extern "C" int lse_moe_route(const void* h, int h_dtype, const float* router, int T, int W, int E,
+                             int has_gate, int top, int* idx, float* wts, float* gate,
+                             cudaStream_t stream) {
+  if (T <= 0) return LSE_OK;
+  if (E <= 0 || top <= 0 || top > E || E > 2048 || (has_gate && !gate)) return LSE_BAD_ARGUMENT;
+  const int blocks = (T + ROUTE_WARPS - 1) / ROUTE_WARPS;
+  const size_t smem = (size_t)ROUTE_WARPS * E * sizeof(float);
+  if (h_dtype == LSE_F32)
+    moe_route_kernel<float><<<blocks, ROUTE_WARPS * 32, smem, stream>>>((const float*)h, router, T, W, E, has_gate,
+                                                                        top, idx, wts, gate);
+  else if (h_dtype == LSE_BF16)
+    moe_route_kernel<bf16><<<blocks, ROUTE_WARPS * 32, smem, stream>>>((const bf16*)h, router, T, W, E, has_gate,
+                                                                       top, idx, wts, gate);
+  else
+    return LSE_BAD_ARGUMENT;
+  return LSE_CHECK_LAUNCH();
+}
+
+extern "C" int lse_moe_sort(const int* idx, int n, int E, int* offsets, int* perm, int* pos_of,
+                            int* tile_batch, int* tile_row0, int* num_tiles, cudaStream_t stream) {
+  if (n <= 0) return LSE_OK;
+  if (E <= 0 || E > 2048) return LSE_BAD_ARGUMENT;
+  const size_t smem = (size_t)(3 * E + 2) * sizeof(int);
+  moe_sort_kernel<<<1, 1024, smem, stream>>>(idx, n, E, offsets, perm, pos_of, tile_batch, tile_row0, num_tiles);
+  return LSE_CHECK_LAUNCH();
+}
+
+extern "C" int lse_moe_combine(const float* y, const int* pos_of, int top, const float* shared_out,
+                               const float* gate, float* out, int accumulate, int T, int W,
+                               cudaStream_t stream) {
+  if (T <= 0) return LSE_OK;
+  if (shared_out && !gate) return LSE_BAD_ARGUMENT;
+  moe_combine_kernel<<<T, 128, 0, stream>>>(y, pos_of, top, shared_out, gate, out, accumulate, W);
+  return LSE_CHECK_LAUNCH();
+}

@@ -359,13 +359,18 @@ __global__ void rope_kv_write_vec_kernel(const TIn* qkv, T* q_out,
 // silu(a) * u. A bfloat16 result keeps 8 bits of mantissa, so the fast exponential and division
 // (relative error near 1e-6) give the same stored value as the exact ones; float32 results use
 // the exact ones.
+// act: LSE_ACT_SILU, or LSE_ACT_GELU_TANH = 0.5 a (1 + tanh(sqrt(2/pi) (a + 0.044715 a^3))).
 template <typename T>
-__device__ __forceinline__ float silu_times(float a, float u) {
+__device__ __forceinline__ float silu_times(float a, float u, int act) {
+  if (act == LSE_ACT_GELU_TANH) {
+    const float inner = 0.7978845608028654f * (a + 0.044715f * a * a * a);
+    return 0.5f * a * (1.f + tanhf(inner)) * u;
+  }
   if constexpr (std::is_same<T, bf16>::value) return __fdividef(a, 1.f + __expf(-a)) * u;
   else return a / (1.f + expf(-a)) * u;
 }
 template <typename TIn, typename T>
-__global__ void silu_mul_kernel(const TIn* __restrict__ gu, T* __restrict__ out, int I) {
+__global__ void silu_mul_kernel(const TIn* __restrict__ gu, T* __restrict__ out, int I, int act) {
   pdl_trigger();
   pdl_wait();
   const size_t t = blockIdx.x;
@@ -378,12 +383,12 @@ __global__ void silu_mul_kernel(const TIn* __restrict__ gu, T* __restrict__ out,
       load4<TIn>(g + i, gv);
       load4<TIn>(u + i, uv);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) gv[j] = silu_times<T>(gv[j], uv[j]);
+      for (int j = 0; j < 4; ++j) gv[j] = silu_times<T>(gv[j], uv[j], act);
       store4<T>(o + i, gv);
     }
   } else {
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < I; i += gridDim.y * blockDim.x) {
-      o[i] = Num<T>::from_float(silu_times<T>(Num<TIn>::to_float(g[i]), Num<TIn>::to_float(u[i])));
+      o[i] = Num<T>::from_float(silu_times<T>(Num<TIn>::to_float(g[i]), Num<TIn>::to_float(u[i]), act));
     }
   }
 }
@@ -393,7 +398,7 @@ __global__ void silu_mul_kernel(const TIn* __restrict__ gu, T* __restrict__ out,
 // vector per thread 15.6 us, two 19.0, four 28.8; the bytes alone take 15.1.)
 template <typename T>
 __global__ void silu_mul_wide_kernel(const T* __restrict__ gu, T* __restrict__ out, int I,
-                                     unsigned total) {
+                                     unsigned total, int act) {
   constexpr int V = Num<T>::kVec;
   pdl_trigger();
   pdl_wait();
@@ -406,7 +411,7 @@ __global__ void silu_mul_wide_kernel(const T* __restrict__ gu, T* __restrict__ o
   Vec16<T> o;
 #pragma unroll
   for (int j = 0; j < V; ++j)
-    o.v[j] = Num<T>::from_float(silu_times<T>(Num<T>::to_float(g.v[j]), Num<T>::to_float(u.v[j])));
+    o.v[j] = Num<T>::from_float(silu_times<T>(Num<T>::to_float(g.v[j]), Num<T>::to_float(u.v[j]), act));
   store16(out + (size_t)t * I + (size_t)c * V, o);
 }
 
@@ -544,8 +549,9 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, void* q_out, int
 }
 
 extern "C" int lse_silu_mul(const void* gu, int in_dtype, void* out, int dtype, int T, int I,
-                            cudaStream_t stream) {
+                            int act, cudaStream_t stream) {
   if (T <= 0 || I <= 0) return LSE_OK;
+  if (act != LSE_ACT_SILU && act != LSE_ACT_GELU_TANH) return LSE_BAD_ARGUMENT;
   const int threads = 256;
   const int vec = in_dtype == LSE_BF16 ? 8 : 4;
   if (in_dtype == dtype && I % vec == 0 && (size_t)T * (I / vec) < (1ull << 31) &&
@@ -553,21 +559,21 @@ extern "C" int lse_silu_mul(const void* gu, int in_dtype, void* out, int dtype, 
     const unsigned total = (unsigned)((size_t)T * (I / vec));
     const unsigned blocks = (total + threads - 1) / threads;
     if (dtype == LSE_F32)
-      launch(silu_mul_wide_kernel<float>, blocks, threads, 0, stream, (const float*)gu, (float*)out, I, total);
+      launch(silu_mul_wide_kernel<float>, blocks, threads, 0, stream, (const float*)gu, (float*)out, I, total, act);
     else
-      launch(silu_mul_wide_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)gu, (bf16*)out, I, total);
+      launch(silu_mul_wide_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)gu, (bf16*)out, I, total, act);
     return LSE_CHECK_LAUNCH();
   }
   const int per_block = threads * 4;
   dim3 grid(T, min((I + per_block - 1) / per_block, 65535));
   if (in_dtype == LSE_F32 && dtype == LSE_F32)
-    launch(silu_mul_kernel<float, float>, grid, threads, 0, stream, (const float*)gu, (float*)out, I);
+    launch(silu_mul_kernel<float, float>, grid, threads, 0, stream, (const float*)gu, (float*)out, I, act);
   else if (in_dtype == LSE_BF16 && dtype == LSE_BF16)
-    launch(silu_mul_kernel<bf16, bf16>, grid, threads, 0, stream, (const bf16*)gu, (bf16*)out, I);
+    launch(silu_mul_kernel<bf16, bf16>, grid, threads, 0, stream, (const bf16*)gu, (bf16*)out, I, act);
   else if (in_dtype == LSE_F32 && dtype == LSE_BF16)
-    launch(silu_mul_kernel<float, bf16>, grid, threads, 0, stream, (const float*)gu, (bf16*)out, I);
+    launch(silu_mul_kernel<float, bf16>, grid, threads, 0, stream, (const float*)gu, (bf16*)out, I, act);
   else if (in_dtype == LSE_FIXED64 && dtype == LSE_BF16 && I % 4 == 0)
-    launch(silu_mul_kernel<fixed64, bf16>, grid, threads, 0, stream, (const fixed64*)gu, (bf16*)out, I);
+    launch(silu_mul_kernel<fixed64, bf16>, grid, threads, 0, stream, (const fixed64*)gu, (bf16*)out, I, act);
   else
     return LSE_BAD_ARGUMENT;
   return LSE_CHECK_LAUNCH();

@@ -10,7 +10,8 @@ from __future__ import annotations
 
 import torch
 
-from ..parts.base import BLOCKS, NORMS, POSITION_ENCODINGS, BuildEnv, ParamDecl, role_dtype, settle
+from ..parts.base import BLOCKS, EMBED_TERMS, NORMS, POSITION_ENCODINGS, BuildEnv, ParamDecl, role_dtype, settle
+from ..parts.base import count_states, flatten_needs
 from .plan import ModelPlan
 
 
@@ -25,6 +26,9 @@ class DecoderModel:
         self.embed_position = (
             POSITION_ENCODINGS.build(plan.embed_position, env) if plan.embed_position is not None else None
         )
+        self.embed_terms = [EMBED_TERMS.build(spec, env) for spec in plan.embed_terms]
+        # the cache layer of the embedding terms' states follows those of the run order
+        self.embed_cache = 1 + max(e.cache for e in plan.run_order)
         self.embed_weight: torch.Tensor | None = None
         self.head_weight: torch.Tensor | None = None
         # which run of the order fills each cache layer
@@ -39,6 +43,9 @@ class DecoderModel:
         for i, block in enumerate(self.blocks):
             for name, decl in block.param_decls().items():
                 decls[f"layers.{i}.{name}"] = decl
+        for i, term in enumerate(self.embed_terms):
+            for name, decl in term.param_decls().items():
+                decls[f"embed_terms.{i}.{name}"] = decl
         for name, decl in self.final_norm.param_decls().items():
             decls[f"final_norm.{name}"] = decl
         if not p.tie_head:
@@ -66,6 +73,9 @@ class DecoderModel:
         for i, block in enumerate(self.blocks):
             prefix = f"layers.{i}."
             block.bind({k[len(prefix):]: v for k, v in params.items() if k.startswith(prefix)})
+        for i, term in enumerate(self.embed_terms):
+            prefix = f"embed_terms.{i}."
+            term.bind({k[len(prefix):]: v for k, v in params.items() if k.startswith(prefix)})
         self.final_norm.bind(
             {k[len("final_norm."):]: v for k, v in params.items() if k.startswith("final_norm.")}
         )
@@ -80,6 +90,7 @@ class DecoderModel:
         for block in self.blocks:
             yield from walk(block)
         yield self.final_norm
+        yield from self.embed_terms
         if self.embed_position is not None:
             yield self.embed_position
 
@@ -96,6 +107,9 @@ class DecoderModel:
                     f"run {k} (layer {e.layer}) reads cache {e.cache}, which holds {needs[e.cache]}, "
                     f"but it needs {need}"
                 )
+        term_needs = tuple(n for t in self.embed_terms for n in flatten_needs(t.cache_need()))
+        if term_needs:
+            needs[self.embed_cache] = term_needs
         return needs
 
     def step_planners(self):
@@ -121,6 +135,12 @@ class DecoderModel:
         x = self.ops.embedding(step.token_ids, self.embed_weight)
         if self.plan.embed_scale != 1.0:
             x *= self.plan.embed_scale
+        if self.embed_terms:
+            view, at = pools.view(self.embed_cache, writes=True), 0
+            for term in self.embed_terms:
+                n = count_states(term.cache_need())
+                term.forward(x, step, view.part(False, at, n))
+                at += n
         if self.embed_position is not None:
             self.embed_position.embed(x, step.positions)  # absolute encodings change x in place
         pending = None

@@ -29,6 +29,9 @@ class ModelPlan:
     final_norm: Any  # norm spec
     tie_head: bool
     embed_position: Any = None  # position-encoding spec applied to the embedded tokens, or None
+    # further terms of the embedding (specs of the EMBED_TERMS registry), added in this order before
+    # embed_position; what they keep per request lies in a cache layer of their own (the last id)
+    embed_terms: tuple[Any, ...] = ()
     # constants that some architectures put around the stack of layers (all off by default):
     embed_scale: float = 1.0  # the embedded tokens are multiplied by this
     logit_scale: float = 1.0  # the logits are multiplied by this ...

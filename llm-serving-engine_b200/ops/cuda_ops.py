@@ -224,10 +224,13 @@ class CudaOps:
     def _sums_taken(self, buf: torch.Tensor) -> None:
         self._sums_live.discard(buf.data_ptr())
 
-    def silu_mul(self, gu, out_dtype=None):
+    _ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+    def silu_mul(self, gu, out_dtype=None, activation="silu"):
+        """``act(gate) * up`` of ``gu = [gate | up]``; ``activation``: silu or gelu_tanh."""
         out_dtype = out_dtype or gu.dtype
         out = torch.empty(gu.shape[0], gu.shape[1] // 2, dtype=out_dtype, device=gu.device)
-        self.ext.silu_mul(gu, out)
+        self.ext.silu_mul(gu, out, self._ACTIVATIONS[activation])
         self.launches += 1
         return out
 
@@ -289,17 +292,17 @@ class CudaOps:
             return torch.addmm(bias, a, w.t())  # bias added before the one rounding to bfloat16
         return torch.mm(a, w.t())
 
-    def gated_silu(self, h, w, bias=None, out_dtype=None):
-        """``silu(h @ gate.T) * (h @ up.T)`` for ``w = [gate rows; up rows]``. With few bfloat16
+    def gated_silu(self, h, w, bias=None, out_dtype=None, activation="silu"):
+        """``act(h @ gate.T) * (h @ up.T)`` for ``w = [gate rows; up rows]``. With few bfloat16
         rows the gate meets its activation as a float32 value (the activation kernel takes the
         product's fixed-point sums); otherwise as the product's rounded output."""
         out_dtype = out_dtype or h.dtype
         if self._few_rows(h, w) and out_dtype == torch.bfloat16 and w.shape[0] % 8 == 0:
             sums = self._product_sums(h, w, bias)
-            out = self.silu_mul(sums, out_dtype=out_dtype)
+            out = self.silu_mul(sums, out_dtype=out_dtype, activation=activation)
             self._sums_taken(sums)
             return out
-        return self.silu_mul(self.linear(h, w, bias), out_dtype=out_dtype)
+        return self.silu_mul(self.linear(h, w, bias), out_dtype=out_dtype, activation=activation)
 
     def project_rope_kv_write(self, h, w, bias, *, num_heads, num_kv_heads, head_dim, positions,
                               token_seq, cos, sin, k_pages, v_pages, block_tables, page_tokens,
@@ -396,9 +399,10 @@ class CudaOps:
 
     def paged_attention(self, q, *, num_heads, num_kv_heads, head_dim, scale, window, k_pages,
                         v_pages, block_tables, page_tokens, step, plan, head_scale=None, slopes=None,
-                        chunk=0):
+                        chunk=0, sinks=None):
         """``head_scale`` / ``slopes`` (float32 ``[heads]``) and ``chunk``: a factor per head on the
-        score, ``slope_h * (i - j)`` taken off it, and keys limited to the query's chunk."""
+        score, ``slope_h * (i - j)`` taken off it, and keys limited to the query's chunk. ``sinks``
+        (float32 ``[heads]``): ``exp(sink_h)`` joins the softmax's denominator."""
         out = torch.empty(q.shape[0], num_heads * head_dim, dtype=q.dtype, device=q.device)
         n_tiles = int(plan["tiles"].shape[0])
         n_dec = int(plan["decode_seqs"].shape[0])
@@ -413,7 +417,7 @@ class CudaOps:
             int(window), block_tables, step.ctx_lens, step.cu_q,
             plan["tiles"] if n_tiles else None, n_tiles,
             plan["decode_seqs"] if n_dec else None, n_dec, splits, scratch,
-            self.attention_kernel, head_scale, slopes, int(chunk),
+            self.attention_kernel, head_scale, slopes, int(chunk), sinks,
         )
         self.launches += (1 if n_tiles else 0) + (1 if n_dec else 0)
         return out
@@ -433,6 +437,75 @@ class CudaOps:
                                     int(norm_dim or head_dim))
         self.launches += 1
         return q
+
+    # ------------------------------------------------------------------ embedding terms, latent attention
+    def hashed_pair_add(self, x, table, state, step, *, buckets, mul_previous, mul_token):
+        """``x[t] += table[(previous * mul_previous + token * mul_token) mod buckets]`` (row
+        ``buckets`` at position 0); ``state`` (int32, one number per slot) hands the last token of
+        a step to the request's next step."""
+        self.ext.hashed_pair_add(x, table, state, step.token_ids, step.positions, step.token_seq, step.cu_q,
+                                 step.state_slots, int(buckets), int(mul_previous), int(mul_token))
+        self.launches += 1
+
+    def sinusoid_add(self, x, positions, freq):
+        """``x[t, 2i] += sin(p freq_i)``, ``x[t, 2i+1] += cos(p freq_i)``."""
+        self.ext.sinusoid_add(x, positions, freq)
+        self.launches += 1
+
+    def latent_write(self, proj, col0, rank, weight, eps, pages, positions, token_seq, block_tables):
+        """Columns ``col0 .. col0 + rank`` of each row of ``proj``, RMS-normed and weighted, into the
+        token's place of ``pages`` ``[pages, 1, page_tokens, >= rank]`` (further dims are zeroed)."""
+        self.ext.latent_write(proj, int(col0), int(rank), weight, float(eps), pages, positions, token_seq,
+                              block_tables)
+        self.launches += 1
+
+    def head_linear(self, a, col0, w, out_dtype):
+        """A product per head: ``out[t, h] = w[h] @ a[t, col0 + h*K : col0 + (h+1)*K]`` for ``w``
+        ``[H, N, K]``; returns ``[T, H*N]``."""
+        out = torch.empty(a.shape[0], w.shape[0] * w.shape[1], dtype=out_dtype, device=a.device)
+        self.ext.head_linear(a, int(col0), w, out)
+        self.launches += 1
+        return out
+
+    # ------------------------------------------------------------------ routed experts
+    def moe_route(self, h, router, num_experts, top, has_gate):
+        """Sigmoid router scores in float32; returns (experts ``[T, top]`` int32, their scores
+        ``[T, top]``, the shared expert's gate ``[T]`` or None)."""
+        T = h.shape[0]
+        idx = torch.empty(T, top, dtype=torch.int32, device=h.device)
+        wts = torch.empty(T, top, dtype=torch.float32, device=h.device)
+        gate = torch.empty(T, dtype=torch.float32, device=h.device) if has_gate else None
+        self.ext.moe_route(h, router, int(num_experts), int(top), idx, wts, gate)
+        self.launches += 1
+        return idx, wts, gate
+
+    def moe_sort(self, idx, num_experts):
+        """The choices sorted by expert, as row ranges and tiles for :meth:`expert_linear` (an
+        opaque int32 work buffer that :meth:`moe_combine` reads too)."""
+        n = idx.numel()
+        tiles = int(self.ext.moe_max_tiles(n, int(num_experts)))
+        work = torch.empty(num_experts + 1 + 2 * n + 2 * tiles + 1, dtype=torch.int32, device=idx.device)
+        self.ext.moe_sort(idx, int(num_experts), work)
+        self.launches += 1
+        return work
+
+    def expert_linear(self, a, w, work, n, top=0, wts=None):
+        """float32 ``[n, N]``: sorted row r is ``w[its expert] @ a-row``. With ``top`` the a-row is
+        gathered, ``a[choice // top] * wts[choice]``; without, ``a`` is already in sorted order."""
+        out = torch.empty(n, w.shape[1], dtype=torch.float32, device=a.device)
+        self.ext.expert_linear(a, w, out, work, int(n), int(top), wts)
+        self.launches += 1
+        return out
+
+    def moe_combine(self, y, work, num_experts, top, shared, gate, residual):
+        """Per token the sum of its experts' rows of ``y`` (+ gate * shared): added into
+        ``residual`` (returns None) or returned."""
+        T = y.shape[0] // top
+        out = residual if residual is not None else torch.empty(T, y.shape[1], dtype=torch.float32, device=y.device)
+        self.ext.moe_combine(y, work, int(num_experts), int(top), shared, gate if shared is not None else None,
+                             out, residual is not None)
+        self.launches += 1
+        return None if residual is not None else out
 
     # ------------------------------------------------------------------ branch-norm blocks, state mixers
     def cast(self, x, dtype):

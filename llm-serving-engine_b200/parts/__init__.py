@@ -1,6 +1,7 @@
 """Parts a model is assembled from. Importing this package registers the built-in kinds."""
 
-from . import attention, blocks, feed_forward, linear_attention, norms, parallel, positions, token_shift  # noqa: F401
+from . import (attention, blocks, embed_terms, feed_forward, latent_attention, linear_attention, moe, norms,  # noqa: F401
+               parallel, positions, token_shift)
 from .attention import AttentionSpec, PagedAttention
 from .base import (
     BLOCKS,
@@ -27,7 +28,10 @@ from .parallel import ParallelMixer, ParallelMixerSpec
 from .token_shift import TokenShift, TokenShiftSpec
 from .feed_forward import SwiGLU, SwiGLUSpec
 from .norms import RMSNorm, RMSNormSpec
-from .positions import NoPositionSpec, RotaryPositionEncoding, RotarySpec
+from .embed_terms import HashedPairEmbedding, HashedPairSpec
+from .latent_attention import LatentAttention, LatentAttentionSpec
+from .moe import RoutedExperts, RoutedExpertsSpec
+from .positions import NoPositionSpec, RotaryPositionEncoding, RotarySpec, SinusoidSpec
 
 __all__ = [
     "AttentionSpec", "PagedAttention", "BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS",
@@ -36,5 +40,6 @@ __all__ = [
     "PreNormBlockSpec", "SwiGLU", "SwiGLUSpec", "RMSNorm", "RMSNormSpec", "NoPositionSpec",
     "RotaryPositionEncoding", "RotarySpec", "INPUT_FILTERS", "BranchNormBlock", "BranchNormBlockSpec",
     "DecayLinearAttention", "DecayLinearAttentionSpec", "ParallelMixer", "ParallelMixerSpec", "TokenShift",
-    "TokenShiftSpec",
+    "TokenShiftSpec", "HashedPairEmbedding", "HashedPairSpec", "LatentAttention", "LatentAttentionSpec",
+    "RoutedExperts", "RoutedExpertsSpec", "SinusoidSpec",
 ]

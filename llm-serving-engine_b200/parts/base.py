@@ -33,7 +33,8 @@ class ParamDecl:
 
     role: ``matrix`` (a projection weight ``[out, in]``), ``embedding`` (``[vocab, width]``),
     ``bias``, ``scale`` (a per-channel weight around one), ``offset`` (a per-channel weight stored
-    around zero, used as one plus itself) or ``mix`` (a per-channel weight between zero and one).
+    around zero, used as one plus itself), ``mix`` (a per-channel weight between zero and one) or
+    ``matrix32`` (a projection whose product is computed in 32-bit in every path: a router).
     The role decides the random draw and the dtype on the device.
     """
 
@@ -41,7 +42,7 @@ class ParamDecl:
     role: str = "matrix"
 
 
-FLOAT32_ROLES = ("scale", "offset", "mix")  # small per-channel tensors read by 32-bit arithmetic
+FLOAT32_ROLES = ("scale", "offset", "mix", "matrix32")  # small per-channel tensors read by 32-bit arithmetic
 
 
 def role_dtype(role: str, compute_dtype: torch.dtype, stored: torch.dtype | None = None) -> torch.dtype:
@@ -89,6 +90,7 @@ class PagedKVNeed:
     window: int = 0
     kind: str = "paged_kv"
     dtype: object = None  # of the pages; None: the model's compute dtype (what the attention kernels here read)
+    values: bool = True  # False: one row per token only (a latent row that serves as key and value alike)
 
 
 @dataclass(frozen=True)
@@ -195,6 +197,19 @@ class PositionEncoding(Part):
 
     def embed(self, x, positions) -> None:
         return None
+
+
+class EmbedTerm(Part):
+    """Something that is added to the embedded tokens before the first layer, beside the token
+    embedding itself: ``forward(x, step, cache)`` adds into the float32 ``x [T, H]`` in place.
+    A term that keeps something per request (the token before a portion, say) declares it with
+    ``cache_need()``; all terms of a model share one cache layer, in the order of the plan."""
+
+    def cache_need(self):
+        return None
+
+    def forward(self, x, step, cache) -> None:  # pragma: no cover - interface
+        raise NotImplementedError
 
 
 class Mixer(Part):
@@ -332,6 +347,7 @@ class Registry:
 
 
 NORMS = Registry("norm")
+EMBED_TERMS = Registry("embedding term")
 INPUT_FILTERS = Registry("input filter")
 POSITION_ENCODINGS = Registry("position encoding")
 MIXERS = Registry("mixer")

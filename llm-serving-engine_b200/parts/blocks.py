@@ -2,7 +2,7 @@
 
 ``prenorm`` (src/llmserve/models/transformer.py:87-94, fused form :176-189):
 
-    x <- x + mixer(norm_in(x));   x <- x + feed_forward(norm_post(x))
+    x <- x + mixer(norm_in(x));   x <- x + feed_forward(norm_post(x))     (the second half is optional)
 
 The residual stream ``x`` is float32 and is updated in place; each add is carried out by the norm
 that reads ``x`` next, so a block returns its feed-forward output as ``pending``: a tensor, None
@@ -29,7 +29,7 @@ from .base import BLOCKS, FEED_FORWARDS, INPUT_FILTERS, MIXERS, NORMS, Block, co
 class PreNormBlockSpec:
     norm_in: Any
     mixer: Any
-    norm_post: Any
+    norm_post: Any  # None together with feed_forward: the layer is its mixer alone
     feed_forward: Any
     kind: str = "prenorm"
 
@@ -41,13 +41,14 @@ class PreNormBlock(Block):
         self.children = {
             "norm_in": NORMS.build(spec.norm_in, env),
             "mixer": MIXERS.build(spec.mixer, env),
-            "norm_post": NORMS.build(spec.norm_post, env),
-            "feed_forward": FEED_FORWARDS.build(spec.feed_forward, env),
         }
+        if spec.feed_forward is not None:
+            self.children["norm_post"] = NORMS.build(spec.norm_post, env)
+            self.children["feed_forward"] = FEED_FORWARDS.build(spec.feed_forward, env)
         self.norm_in = self.children["norm_in"]
         self.mixer = self.children["mixer"]
-        self.norm_post = self.children["norm_post"]
-        self.feed_forward = self.children["feed_forward"]
+        self.norm_post = self.children.get("norm_post")
+        self.feed_forward = self.children.get("feed_forward")
 
     def forward(self, x, pending, step, cache):
         h = self.norm_in.forward(x, settle(pending, self.norm_in))
@@ -55,6 +56,8 @@ class PreNormBlock(Block):
             a = self.mixer.forward(h, step, cache, residual=x, may_defer=True)  # None: already added into x
         else:
             a = self.mixer.forward(h, step, cache)
+        if self.feed_forward is None:
+            return x, a
         h = self.norm_post.forward(x, settle(a, self.norm_post))
         if getattr(self.feed_forward, "accepts_residual", False):
             return x, self.feed_forward.forward(h, step, residual=x, may_defer=True)

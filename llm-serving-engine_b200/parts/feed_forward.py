@@ -1,7 +1,8 @@
 """Dense gated feed-forward (src/llmserve/models/transformer.py:62-71).
 
     gu = h @ Wgu^T          rows of Wgu: gate (first I rows), then up (last I rows)
-    y  = (silu(gate) * up) @ Wdown^T,    silu(g) = g / (1 + exp(-g))
+    y  = (act(gate) * up) @ Wdown^T,     act = silu: g / (1 + exp(-g)), or
+                                         gelu_tanh: 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))
 
 No biases. The activation is computed in float32 (src/llmserve/kernels/csrc/fused_ops.cpp:75-91).
 """
@@ -18,6 +19,7 @@ class SwiGLUSpec:
     hidden_size: int
     intermediate_size: int
     kind: str = "swiglu"
+    activation: str = "silu"  # or "gelu_tanh"
 
 
 @FEED_FORWARDS.register("swiglu")
@@ -29,6 +31,11 @@ class SwiGLU(FeedForward):
             "down.weight": ParamDecl((s.hidden_size, s.intermediate_size), "matrix"),
         }
 
+    def __init__(self, spec: SwiGLUSpec, env) -> None:
+        super().__init__(spec, env)
+        if spec.activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"gated feed-forward: activation {spec.activation!r} is not known")
+
     def bind(self, params):
         self.gate_up_weight = params["gate_up.weight"]
         self.down_weight = params["down.weight"]
@@ -37,5 +44,9 @@ class SwiGLU(FeedForward):
 
     def forward(self, h, step, residual=None, may_defer=False):
         ops = self.ops
-        a = ops.gated_silu(h, self.gate_up_weight, None, out_dtype=self.env.dtype)
+        if self.spec.activation == "silu":
+            a = ops.gated_silu(h, self.gate_up_weight, None, out_dtype=self.env.dtype)
+        else:
+            a = ops.gated_silu(h, self.gate_up_weight, None, out_dtype=self.env.dtype,
+                               activation=self.spec.activation)
         return project_into(ops, a, self.down_weight, None, self.env.residual_dtype, residual, may_defer)

@@ -1,0 +1,127 @@
+"""Attention over a cached low-rank latent row per token, with a window and a sink per head.
+
+Per token, with ``h`` the normed input, H heads of ``head_dim`` query/key dims and ``value_dim``
+value dims, and a latent of ``latent_rank`` dims:
+
+    q      = Wq h                                         [H, head_dim]
+    c      = w_c * d / sqrt(mean(d^2) + eps),  d = Wd h   the cached latent row [latent_rank]
+    k_j    = Wuk c_j,   v_j = Wuv c_j                      per head, never materialised
+    s_j    = scale * q . k_j      for the keys j of the window (the last ``window`` positions,
+                                  the query's own included; 0: all earlier ones)
+    p_j    = exp(s_j) / (exp(sink) + sum_i exp(s_i))      sink: a learned number per head
+    out    = Wo concat_heads(sum_j p_j v_j)
+
+Only ``c`` is kept per token: one row of the cache serves as key and as value. The products with
+``Wuk`` and ``Wuv`` are moved to the query's side, ``q . (Wuk c) = (Wuk^T q) . c`` and
+``sum_j p_j Wuv c_j = Wuv (sum_j p_j c_j)``, so the attention kernels see H query heads of
+``latent_rank`` dims on one shared key/value head. A latent rank that is no multiple of 16 is
+padded with zeros when the weights are bound.
+
+A layer with ``own_latent=False`` has no ``Wd``: it is bound to the cache layer of another layer
+and reads the rows that layer wrote, with its own ``Wuk``, ``Wuv``, queries, window and sinks.
+``cache_window`` is what the shared cache keeps (at least every reader's window).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .base import MIXERS, Mixer, PagedKVNeed, ParamDecl, project_into
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    value_dim: int
+    latent_rank: int
+    scale: float
+    eps: float  # of the latent row's norm
+    window: int = 0  # 0: every earlier token
+    cache_window: int = 0  # what the cache layer keeps: 0 or >= the window of every layer that reads it
+    own_latent: bool = True
+    sinks: bool = True
+    kind: str = "latent_attention"
+
+
+@MIXERS.register("latent_attention")
+class LatentAttention(Mixer):
+    accepts_residual = True
+
+    def __init__(self, spec: LatentAttentionSpec, env) -> None:
+        super().__init__(spec, env)
+        if spec.cache_window and (spec.window == 0 or spec.window > spec.cache_window):
+            raise ValueError("latent_attention: the cache keeps fewer tokens than the window reads")
+        self.q_size = spec.num_heads * spec.head_dim
+        self.pad = (-spec.latent_rank) % 16
+        self.kernel_dim = spec.latent_rank + self.pad
+        env.ops.check_attention_shape(self.kernel_dim, env.dtype, spec.num_heads, 1)
+
+    def param_decls(self):
+        s = self.spec
+        rows = self.q_size + (s.latent_rank if s.own_latent else 0)
+        decls = {
+            "in.weight": ParamDecl((rows, s.hidden_size), "matrix"),  # q rows, then the latent's
+            "uk.weight": ParamDecl((self.q_size, s.latent_rank), "matrix"),
+            "uv.weight": ParamDecl((s.num_heads * s.value_dim, s.latent_rank), "matrix"),
+            "o.weight": ParamDecl((s.hidden_size, s.num_heads * s.value_dim), "matrix"),
+        }
+        if s.own_latent:
+            decls["latent_norm.weight"] = ParamDecl((s.latent_rank,), "scale")
+        if s.sinks:
+            decls["sink"] = ParamDecl((s.num_heads,), "offset")
+        return decls
+
+    def bind(self, params):
+        s = self.spec
+        H, R = s.num_heads, s.latent_rank
+        self.in_weight = params["in.weight"]
+        self.o_weight = params["o.weight"]
+        self.latent_norm_weight = params.get("latent_norm.weight")
+        self.sink = params.get("sink")
+        # the query side's products, per head as [out, in]: Wuk^T [H, R(+pad), head_dim] and
+        # Wuv [H, value_dim, R(+pad)]
+        uk_t = params["uk.weight"].view(H, s.head_dim, R).transpose(1, 2)
+        uv = params["uv.weight"].view(H, s.value_dim, R)
+        if self.pad:
+            uk_t = torch.nn.functional.pad(uk_t, (0, 0, 0, self.pad))
+            uv = torch.nn.functional.pad(uv, (0, self.pad))
+        self.uk_t = uk_t.contiguous()
+        self.uv = uv.contiguous()
+
+    def cache_need(self):
+        return PagedKVNeed(1, self.kernel_dim, self.spec.cache_window, values=False)
+
+    def reserve(self, max_seqs: int) -> None:
+        if hasattr(self.ops, "reserve_attention_scratch"):
+            self.ops.reserve_attention_scratch(self.kernel_dim, max_seqs, self.spec.num_heads)
+
+    def plan_key(self):
+        return ("attention", self.env.dtype, self.kernel_dim)
+
+    def plan_step(self, host_step, group):
+        return self.ops.attention_plan(host_step, self.env.dtype, self.kernel_dim)
+
+    def plan_rows(self, single: int, portions: int, tokens: int) -> dict[str, int]:
+        qt = self.ops.attention_q_tile(self.env.dtype, self.kernel_dim)
+        return {"tiles": tokens // qt + portions, "decode_seqs": single}
+
+    def forward(self, h, step, cache, residual=None, may_defer=False):
+        s, ops = self.spec, self.ops
+        tables = step.block_tables[cache.group]
+        proj = ops.linear(h, self.in_weight, None, out_dtype=torch.float32)  # q | latent, unrounded
+        if s.own_latent:
+            if not cache.writes:
+                raise RuntimeError("a latent-attention layer with its own latent must fill its cache layer")
+            ops.latent_write(proj, self.q_size, s.latent_rank, self.latent_norm_weight, s.eps, cache.k,
+                             step.positions, step.token_seq, tables)
+        q = ops.head_linear(proj, 0, self.uk_t, out_dtype=self.env.dtype)  # [T, H * rank]
+        o = ops.paged_attention(
+            q, num_heads=s.num_heads, num_kv_heads=1, head_dim=self.kernel_dim, scale=s.scale,
+            window=s.window, k_pages=cache.k, v_pages=cache.v, block_tables=tables,
+            page_tokens=cache.page_tokens, step=step, plan=step.plans[self.plan_key()], sinks=self.sink)
+        o = ops.head_linear(o, 0, self.uv, out_dtype=self.env.dtype)  # [T, H * value_dim]
+        return project_into(ops, o, self.o_weight, None, self.env.residual_dtype, residual, may_defer)

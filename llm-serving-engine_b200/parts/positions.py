@@ -7,6 +7,11 @@ angles are never rounded to 16 bits. Frequency scaling ``linear`` and ``llama3``
 src/llmserve/models/layers.py:24-58.
 
 ``none``: no position information (for mixers that carry order in their own state).
+
+``sinusoid``: an absolute encoding added to the embedded tokens: entry 2i of the vector of
+position p is ``sin(p * base^(-2i/width))`` and entry 2i+1 the cosine of the same angle. The
+frequencies are made once in float64 and stored in float32; the angle is the float32 product of
+the position and the frequency.
 """
 
 from __future__ import annotations
@@ -72,6 +77,25 @@ class RotaryPositionEncoding(PositionEncoding):
 
     def rotary_tables(self):
         return self.cos, self.sin
+
+
+@dataclass(frozen=True)
+class SinusoidSpec:
+    hidden_size: int
+    base: float = 10000.0
+    kind: str = "sinusoid"
+
+
+@POSITION_ENCODINGS.register("sinusoid")
+class SinusoidPositionEncoding(PositionEncoding):
+    def __init__(self, spec: SinusoidSpec, env) -> None:
+        super().__init__(spec, env)
+        w = spec.hidden_size
+        i = torch.arange((w + 1) // 2, dtype=torch.float64)
+        self.freq = (spec.base ** (-2.0 * i / w)).float().contiguous().to(env.device)
+
+    def embed(self, x, positions) -> None:
+        self.ops.sinusoid_add(x, positions, self.freq)
 
 
 @POSITION_ENCODINGS.register("none")

@@ -61,9 +61,13 @@ class PlainOps:
         y = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * weight
         return y.to(out_dtype)
 
-    def silu_mul(self, gu, out_dtype=None):
+    def silu_mul(self, gu, out_dtype=None, activation="silu"):
         g, u = gu.float().chunk(2, dim=-1)
-        return (g / (1 + torch.exp(-g)) * u).to(out_dtype or gu.dtype)
+        if activation == "gelu_tanh":
+            act = 0.5 * g * (1 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
+        else:
+            act = g / (1 + torch.exp(-g))
+        return (act * u).to(out_dtype or gu.dtype)
 
     def linear(self, a, w, bias=None, out_dtype=None, accumulate_into=None):
         y = a.float() @ w.float().T
@@ -74,8 +78,9 @@ class PlainOps:
             return None
         return y.to(out_dtype or a.dtype)
 
-    def gated_silu(self, h, w, bias=None, out_dtype=None):
-        return self.silu_mul(self.linear(h, w, bias, out_dtype=torch.float32), out_dtype=out_dtype or h.dtype)
+    def gated_silu(self, h, w, bias=None, out_dtype=None, activation="silu"):
+        return self.silu_mul(self.linear(h, w, bias, out_dtype=torch.float32), out_dtype=out_dtype or h.dtype,
+                             activation=activation)
 
     # ------------------------------------------------------------------ attention
     def project_rope_kv_write(self, h, w, bias, *, out_dtype=None, **kw):
@@ -132,7 +137,7 @@ class PlainOps:
 
     def paged_attention(self, q, *, num_heads, num_kv_heads, head_dim, scale, window, k_pages,
                         v_pages, block_tables, page_tokens, step, plan=None, head_scale=None,
-                        slopes=None, chunk=0):
+                        slopes=None, chunk=0, sinks=None):
         T, D = q.shape[0], head_dim
         qkv = q
         q = q[:, : num_heads * D].float().reshape(T, num_heads, D)
@@ -159,6 +164,9 @@ class PlainOps:
             if slopes is not None:
                 sc = sc - slopes.float()[:, None, None] * (qpos - j[None, :]).float()[None]
             sc = sc.masked_fill(~visible, float("-inf"))
+            if sinks is not None:  # a column without a value
+                sc = torch.cat([sc, sinks.float()[:, None, None].expand(-1, n, 1)], -1)
+                v = torch.cat([v, torch.zeros_like(v[:1])], 0)
             out[a:b] = torch.einsum("hts,shd->thd", sc.softmax(-1), v)
         return out.view(T, num_heads * D).to(qkv.dtype)
 
@@ -186,6 +194,61 @@ class PlainOps:
             k_pages[page, :, off] = k.to(k_pages.dtype)
             v_pages[page, :, off] = v.to(v_pages.dtype)
         return q.to(out_dtype).reshape(T, num_heads * D).contiguous()
+
+    # ------------------------------------------------------------------ embedding terms, latent attention
+    def hashed_pair_add(self, x, table, state, step, *, buckets, mul_previous, mul_token):
+        ids, pos = step.token_ids.tolist(), step.positions.tolist()
+        cu, slots = step.cu_q.tolist(), step.state_slots.tolist()
+        for s_ in range(len(slots)):
+            prev = int(state[slots[s_], 0])
+            for t in range(cu[s_], cu[s_ + 1]):
+                row = buckets if pos[t] == 0 else (prev * mul_previous + ids[t] * mul_token) % buckets
+                x[t] += table[row].float()
+                prev = ids[t]
+            state[slots[s_], 0] = prev
+
+    def sinusoid_add(self, x, positions, freq):
+        ang = positions.float()[:, None] * freq[None, :]
+        w = x.shape[1]
+        x[:, 0::2] += torch.sin(ang)[:, : (w + 1) // 2]
+        x[:, 1::2] += torch.cos(ang)[:, : w // 2]
+
+    def latent_write(self, proj, col0, rank, weight, eps, pages, positions, token_seq, block_tables):
+        d = proj[:, col0 : col0 + rank].float()
+        c = d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + eps) * weight
+        pos = positions.long()
+        page_tokens = pages.shape[2]
+        page = block_tables[token_seq.long(), pos // page_tokens].long()
+        pages[page, 0, pos % page_tokens] = 0
+        pages[page, 0, pos % page_tokens, :rank] = c.to(pages.dtype)
+
+    def head_linear(self, a, col0, w, out_dtype):
+        H, N, K = w.shape
+        x = a[:, col0 : col0 + H * K].float().view(-1, H, K)
+        return torch.einsum("thk,hnk->thn", x, w.float()).reshape(-1, H * N).to(out_dtype)
+
+    # ------------------------------------------------------------------ routed experts
+    def moe_route(self, h, router, num_experts, top, has_gate):
+        z = torch.sigmoid(h.float() @ router.float().T)
+        val, idx = torch.topk(z[:, :num_experts], top, dim=-1)
+        return idx.to(torch.int32), val, (z[:, num_experts] if has_gate else None)
+
+    def moe_sort(self, idx, num_experts):
+        return idx  # the plain products below walk the choices as they are
+
+    def expert_linear(self, a, w, work, n, top=0, wts=None):
+        idx = work.reshape(-1).long()
+        rows = a.float() if top == 0 else a.float().repeat_interleave(top, 0) * wts.reshape(-1, 1)
+        return torch.einsum("rk,rnk->rn", rows, w.float()[idx])
+
+    def moe_combine(self, y, work, num_experts, top, shared, gate, residual):
+        out = y.view(-1, top, y.shape[1]).sum(1)
+        if shared is not None:
+            out = out + gate[:, None] * shared.float()
+        if residual is not None and self.accumulate:
+            residual += out
+            return None
+        return out
 
     # ------------------------------------------------------------------ branch-norm blocks, state mixers
     def cast(self, x, dtype):
