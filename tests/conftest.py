@@ -154,3 +154,88 @@ def write_gubotar(folder, name, spread=True):
 @pytest.fixture(scope="session")
 def gubotar_dirs(tmp_path_factory):
     return {name: write_gubotar(tmp_path_factory.mktemp(f"gubotar-{name}"), name) for name in GUBOTAR_TINY}
+
+
+# ---- Pazivik: small configurations that differ in every size, in the order of layers and in which
+# optional thing is there.
+def _lat(heads, dim, vdim, rank, scale, window, mlp, kv_from=None):
+    m = {"heads": heads, "dim": dim, "vdim": vdim, "kv_rank": rank, "scale": scale}
+    if window:
+        m["mask"] = {"size": window}
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return {"type": "latent_attention", "mixer": m, "mlp": mlp}
+
+
+def _moe(experts, top, ff, shared):
+    d = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}}
+    if shared:
+        d["shared"] = {"ff": shared}
+    return d
+
+
+def _dense(ff):
+    return {"kind": "dense", "ff": ff}
+
+
+PAZIVIK_TINY = {
+    # a reader whose window is wider than its writer's; two experts per token; a latent rank that
+    # is no multiple of 16; a layer without feed-forward; experts without a shared one
+    "P1": dict(seed=4, page_tokens=16, config={
+        "architecture": "Pazivik", "vocab": 211, "width": 96, "norm": {"eps": 1e-5}, "logit_softcap": 20.0,
+        "embedding": {"bigram": {"buckets": 97, "mul_cur": 5, "mul_prev": 31}},
+        "layers": [_lat(3, 16, 24, 32, 0.3, 20, _dense(160)),
+                   _lat(2, 32, 8, 32, 0.2, 33, _moe(5, 2, 24, 40), kv_from=0),
+                   _lat(4, 8, 16, 40, 0.5, 7, None),
+                   _lat(1, 48, 20, 40, 0.15, 7, _moe(3, 1, 32, 0), kv_from=2)]}),
+    # widths that are multiples of nothing; a window shorter than a page; a layer without a mask;
+    # every expert chosen; one bucket; no soft cap; a reader that follows its writer at a distance
+    "P2": dict(seed=11, page_tokens=8, config={
+        "architecture": "Pazivik", "vocab": 130, "width": 70, "norm": {"eps": 1e-6},
+        "embedding": {"bigram": {"buckets": 1, "mul_cur": 3, "mul_prev": 2}},
+        "layers": [_lat(1, 24, 20, 16, 0.25, 5, _dense(50)),
+                   _lat(5, 8, 12, 48, 0.4, 0, _moe(4, 4, 10, 16)),
+                   _lat(2, 20, 6, 16, 0.3, 9, _dense(30), kv_from=0)]}),
+    # the head and latent sizes of larger models; many experts; a window of exactly one page and
+    # one of several pages; big multipliers of the bigram hash
+    "P3": dict(seed=17, page_tokens=32, sharp=8, config={
+        "architecture": "Pazivik", "vocab": 300, "width": 128, "norm": {"eps": 1e-5}, "logit_softcap": 50.0,
+        "embedding": {"bigram": {"buckets": 509, "mul_cur": 1000003, "mul_prev": 999983}},
+        "layers": [_lat(8, 64, 32, 128, 0.125, 32, _moe(16, 3, 48, 64)),
+                   _lat(4, 32, 64, 64, 0.18, 100, _dense(192)),
+                   _lat(6, 16, 16, 64, 0.25, 64, _moe(2, 1, 64, 8), kv_from=1)]}),
+}
+
+
+def write_pazivik(folder, name):
+    """A random Pazivik folder whose weights are drawn wide: attention is far from flat, sinks,
+    norms and gates differ clearly from head to head, so that leaving one of them out, or reading
+    a key too many, changes the logits clearly."""
+    from safetensors.torch import load_file, save_file
+
+    from llmserve_b200.config.pazivik import PazivikConfig
+    from llmserve_b200.weights import write_random_model
+
+    spec = PAZIVIK_TINY[name]
+    write_random_model(folder, PazivikConfig.from_dict(spec["config"]), spec["seed"])
+    f = folder / "model.safetensors"
+    t = load_file(str(f))
+    g = torch.Generator().manual_seed(spec["seed"] + 1)
+    for k, v in t.items():
+        if k.endswith("sink"):
+            t[k] = (4 * (torch.rand(v.shape, generator=g) - 0.5)).to(v.dtype)
+        elif v.dim() == 1:
+            t[k] = (1.0 + (torch.rand(v.shape, generator=g) - 0.5)).to(v.dtype)
+        elif k in ("embed", "bigram"):
+            t[k] = (v.float() * 40).to(v.dtype)
+        elif k.endswith("mix.q") or k.endswith("mix.uk"):
+            t[k] = (v.float() * spec.get("sharp", 25)).to(v.dtype)  # wider heads need less to be sharp
+        else:
+            t[k] = (v.float() * 8).to(v.dtype)
+    save_file(t, str(f))
+    return folder
+
+
+@pytest.fixture(scope="session")
+def pazivik_dirs(tmp_path_factory):
+    return {name: write_pazivik(tmp_path_factory.mktemp(f"pazivik-{name}"), name) for name in PAZIVIK_TINY}

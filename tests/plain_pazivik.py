@@ -145,3 +145,29 @@ def forward(tokens, w, cfg, return_layers=False):
     if cap:
         logits = cap * torch.tanh(logits / cap)
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+# ----------------------------------------------------------------------------- a model folder
+def load(folder):
+    import json
+    from pathlib import Path
+
+    from safetensors.torch import load_file
+
+    folder = Path(folder)
+    cfg = json.loads((folder / "config.json").read_text())
+    return cfg, {k: v.to(F64) if v.is_floating_point() else v for k, v in load_file(str(folder / "model.safetensors")).items()}
+
+
+def model_logits(folder, tokens):
+    cfg, w = load(folder)
+    return forward(list(tokens), w, cfg).float()
+
+
+def greedy(folder, prompt, n):
+    """n tokens generated greedily after ``prompt`` (the whole sequence is run again each time)."""
+    cfg, w = load(folder)
+    tokens = list(prompt)
+    for _ in range(n):
+        tokens.append(int(forward(tokens, w, cfg)[-1].argmax()))
+    return tokens[len(prompt):]
