@@ -210,7 +210,13 @@ PAZIVIK_TINY = {
 def write_pazivik(folder, name):
     """A random Pazivik folder whose weights are drawn wide: attention is far from flat, sinks,
     norms and gates differ clearly from head to head, so that leaving one of them out, or reading
-    a key too many, changes the logits clearly."""
+    a key too many, changes the logits clearly.
+
+    No routing decision is a close call (a model computed in bfloat16 must pick the same experts
+    as the float64 one): the last dims of the residual stream carry, for every token, one of
+    evenly spaced levels per expert, in an order that depends on the token; no layer writes
+    those dims, and each router row reads its expert's dim with weight one beside small random
+    weights on all the others."""
     from safetensors.torch import load_file, save_file
 
     from llmserve_b200.config.pazivik import PazivikConfig
@@ -232,6 +238,26 @@ def write_pazivik(folder, name):
             t[k] = (v.float() * spec.get("sharp", 25)).to(v.dtype)  # wider heads need less to be sharp
         else:
             t[k] = (v.float() * 8).to(v.dtype)
+    cfg = spec["config"]
+    width = cfg["width"]
+    moe = [(i, l["mlp"]["router"]["experts"]) for i, l in enumerate(cfg["layers"])
+           if l["mlp"] is not None and l["mlp"]["kind"] == "moe"]
+    most = max(e for _, e in moe)
+    step = next(m for m in (3, 5, 7, 11) if all(most % q or m % q for q in (2, 3, 5, 7, 11)))
+    dims = [width - 2 * most + 2 * e for e in range(most)]  # even entries: the sinusoid adds next to nothing there
+    spacing = 1.5 if most <= 8 else 1.0
+    tok = torch.arange(cfg["vocab"])[:, None]
+    levels = spacing * (((tok * 7 + step * torch.arange(most)[None, :]) % most).float() - (most - 1) / 2)
+    t["embed"][:, dims] = levels.to(t["embed"].dtype)
+    t["bigram"][:, dims] = 0
+    for k in t:
+        if k.endswith("mix.o") or k.endswith("down"):
+            t[k][dims, :] = 0
+    for i, experts in moe:
+        t[f"l{i}.norm2"][dims] = 1
+        router = torch.randn(experts, width, generator=g) * 0.002
+        router[torch.arange(experts), dims[:experts]] = 1.0
+        t[f"l{i}.mlp.router"] = router.to(torch.bfloat16)
     save_file(t, str(f))
     return folder
 
