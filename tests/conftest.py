@@ -235,7 +235,7 @@ def write_pazivik(folder, name):
         elif k in ("embed", "bigram"):
             t[k] = (v.float() * 40).to(v.dtype)
         elif k.endswith("mix.q") or k.endswith("mix.uk"):
-            t[k] = (v.float() * spec.get("sharp", 25)).to(v.dtype)  # wider heads need less to be sharp
+            t[k] = (v.float() * spec.get("sharp", 10)).to(v.dtype)  # wider heads need less to be sharp
         else:
             t[k] = (v.float() * 8).to(v.dtype)
     cfg = spec["config"]

@@ -278,7 +278,7 @@ def gpu_runner(folder, name, num_pages, dtype, max_num_seqs=4, max_len=512):
 
 
 LENGTHS = {"P1": [5, 70, 1, 33, 49, 126, 2], "P2": [2, 40, 9, 64, 17, 100], "P3": [3, 150, 18, 77, 230]}
-TOL = {"float32": (2e-4, 2e-5), "bfloat16": (0.0, 0.03)}  # (absolute, relative to the largest logit)
+TOL = {"float32": (2e-4, 5e-5), "bfloat16": (0.0, 0.03)}  # (absolute, relative to the largest logit)
 
 
 @pytest.fixture(scope="module")
