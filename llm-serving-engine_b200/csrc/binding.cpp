@@ -471,7 +471,7 @@ void latent_write(const Tensor& proj, int64_t col0, int64_t R, const Tensor& wei
 }
 
 // out[t, h, :] = w[h] . a[t, col0 + h*K : col0 + (h+1)*K]     w [H, N, K], out [T, H*N]
-void head_linear(const Tensor& a, int64_t col0, const Tensor& w, Tensor& out) {
+void head_linear(const Tensor& a, int64_t col0, const Tensor& w, Tensor& out, int64_t kind) {
   check_cuda(a, "a");
   check_cuda(w, "w");
   check_cuda(out, "out");
@@ -480,7 +480,7 @@ void head_linear(const Tensor& a, int64_t col0, const Tensor& w, Tensor& out) {
   TORCH_CHECK(col0 >= 0 && col0 + H * K <= a.size(1) && out.size(0) == a.size(0) && out.size(1) == H * N,
               "head_linear: shapes disagree");
   done(lse_head_linear(a.data_ptr(), out_code(a, "a"), a.size(1), col0, w.data_ptr(), out_code(w, "w"),
-                       out.data_ptr(), out_code(out, "out"), (int)a.size(0), (int)H, (int)N, (int)K, stream()),
+                       out.data_ptr(), out_code(out, "out"), (int)a.size(0), (int)H, (int)N, (int)K, (int)kind, stream()),
        "head_linear");
 }
 
@@ -523,7 +523,7 @@ void moe_sort(const Tensor& idx, int64_t E, Tensor& work) {
 
 // out[r] = w[expert of sorted row r] . a-row(r); gather: a-row(r) = a[choice / top] * wts[choice]
 void expert_linear(const Tensor& a, const Tensor& w, Tensor& out, const Tensor& work, int64_t n, int64_t top,
-                   const OptTensor& wts) {
+                   const OptTensor& wts, int64_t kind) {
   check_cuda(a, "a");
   check_cuda(w, "w");
   check_f32(out, "out");
@@ -545,7 +545,7 @@ void expert_linear(const Tensor& a, const Tensor& w, Tensor& out, const Tensor& 
   done(lse_expert_linear(a.data_ptr(), out_code(a, "a"), a.size(1), gather ? p + E + 1 : nullptr,
                          gather ? (int)top : 1, sc, w.data_ptr(), out_code(w, "w"), out.data_ptr<float>(),
                          (int)n, (int)w.size(1), (int)w.size(2), p, p + E + 1 + 2 * n, p + E + 1 + 2 * n + mt,
-                         p + E + 1 + 2 * n + 2 * mt, (int)mt, stream()),
+                         p + E + 1 + 2 * n + 2 * mt, (int)mt, (int)kind, stream()),
        "expert_linear");
 }
 

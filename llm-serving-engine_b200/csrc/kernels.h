@@ -192,8 +192,11 @@ int lse_latent_write(const void* proj, int in_dtype, long long stride, int col0,
 // A product per head: out[t, h*N + n] = sum_k a[t*a_stride + a_col0 + h*K + k] * w[(h*N + n)*K + k]
 // with float32 accumulation in ascending k by one thread (a row's result does not depend on T).
 // Served: (a, w, out) = (f32, f32, f32), (f32 | bf16, bf16, bf16 | f32).
+// kind: 0 = CUDA cores; 1 = mma.sync tensor-core tiles; 2 = a kernel for few rows that streams the
+// weights once. 1 and 2 need bfloat16 a and w with K, a_stride and a_col0 multiples of 8 (else the
+// call is served as kind 0).
 int lse_head_linear(const void* a, int a_dtype, long long a_stride, long long a_col0, const void* w,
-                    int w_dtype, void* out, int out_dtype, int T, int H, int N, int K,
+                    int w_dtype, void* out, int out_dtype, int T, int H, int N, int K, int kind,
                     cudaStream_t stream);
 
 // Routed experts. h [T, W]; router float32 [E (+1), W].
@@ -204,7 +207,8 @@ int lse_head_linear(const void* a, int a_dtype, long long a_stride, long long a_
 //     expert each (tile_batch, tile_row0: room for n / tile_rows + E entries; num_tiles [1]).
 //   lse_expert_linear: out[r, :] = w[expert of r] . arow(r) for every sorted row r, float32 out
 //     [rows, N]; arow(r) = a[a_rows[r] / a_div] * a_scale[a_rows[r]] (a_rows null: a[r], unscaled);
-//     w [E, N, K]. Launched for max_tiles tiles; tiles beyond *num_tiles do nothing.
+//     w [E, N, K]. Launched for max_tiles tiles; tiles beyond *num_tiles do nothing. kind as above
+//     (kinds 1 and 2 multiply the float32 sums by a_scale, which is the same product).
 //   lse_moe_combine: out[t] (+)= sum_k y[pos_of[t*top + k]] (+ gate[t] * shared_out[t]).
 int lse_moe_tile_rows(void);
 int lse_moe_route(const void* h, int h_dtype, const float* router, int T, int W, int E, int has_gate,
@@ -214,7 +218,7 @@ int lse_moe_sort(const int* idx, int n, int E, int* offsets, int* perm, int* pos
 int lse_expert_linear(const void* a, int a_dtype, long long a_stride, const int* a_rows, int a_div,
                       const float* a_scale, const void* w, int w_dtype, float* out, int rows, int N,
                       int K, const int* offsets, const int* tile_batch, const int* tile_row0,
-                      const int* num_tiles, int max_tiles, cudaStream_t stream);
+                      const int* num_tiles, int max_tiles, int kind, cudaStream_t stream);
 int lse_moe_combine(const float* y, const int* pos_of, int top, const float* shared_out,
                     const float* gate, float* out, int accumulate, int T, int W, cudaStream_t stream);
 }

@@ -189,6 +189,227 @@ __global__ void __launch_bounds__(256) rows_gemm_kernel(const RowsGemm g) {
   }
 }
 
+// ------------------------------------------------------------------------------------ rows_gemm, bfloat16
+// The same products for bfloat16 operands whose rows are whole 16-byte vectors (K, the row
+// strides and the column offsets multiples of 8). out_scale: the result of logical row r is
+// multiplied by a_scale[a_rows[r]] (a product is linear in its input, so scaling the input row
+// is scaling the result; here it is done in float32 on the sums).
+//
+// rows_gemm_mma: 64 rows x 128 columns per block on mma.sync tensor cores (m16n8k16, float32
+// accumulation), 8 warps of 32 x 32, operand tiles of 32 k brought by cp.async into two buffers.
+constexpr int MM_BN = 128, MM_BK = 32, MM_LD = MM_BK + 8, MM_THREADS = 256;
+
+__device__ __forceinline__ void rg_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void rg_mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void rg_cp_async16(void* smem, const void* gmem, bool valid) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(addr), "l"(gmem), "r"(bytes));
+}
+
+// Which rows a block works on (shared by the kernels of this file): tile or grid position.
+__device__ __forceinline__ bool rows_of_block(const RowsGemm& g, int& batch, int& m0, int& m_end) {
+  if (g.tile_batch) {
+    if ((int)blockIdx.y >= *g.num_tiles) return false;
+    batch = g.tile_batch[blockIdx.y];
+    m0 = g.tile_row0[blockIdx.y];
+    m_end = min(g.offsets[batch + 1], m0 + BM);
+  } else {
+    batch = blockIdx.z;
+    m0 = blockIdx.y * BM;
+    m_end = min(g.T, m0 + BM);
+  }
+  return true;
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(MM_THREADS) rows_gemm_mma_kernel(const RowsGemm g) {
+  __shared__ __align__(16) bf16 As[2][BM][MM_LD];
+  __shared__ __align__(16) bf16 Bs[2][MM_BN][MM_LD];
+  __shared__ int srow[BM];
+  __shared__ float sscale[BM];
+  const int tid = threadIdx.x;
+  int batch, m0, m_end;
+  if (!rows_of_block(g, batch, m0, m_end)) return;
+  if (tid < BM) {
+    const int r = m0 + tid;
+    int row = -1;
+    float sc = 1.f;
+    if (r < m_end) {
+      const int idx = g.a_rows ? g.a_rows[r] : r;
+      row = g.a_rows ? idx / g.a_div : r;
+      if (g.a_scale) sc = g.a_scale[idx];
+    }
+    srow[tid] = row;
+    sscale[tid] = sc;
+  }
+  __syncthreads();
+  const int N = g.N, K = g.K;
+  const int n0 = blockIdx.x * MM_BN;
+  const bf16* a = (const bf16*)g.a + g.a_col0 + (long long)batch * g.a_batch_cols;
+  const bf16* w = (const bf16*)g.w + (long long)batch * g.w_batch_stride;
+  const int warp = tid >> 5, lane = tid & 31, gq = lane >> 2, t4 = lane & 3;
+  const int wm = (warp >> 2) * 32, wn = (warp & 3) * 32;
+
+  auto load_tiles = [&](int buf, int k0) {
+    // A: 64 rows x 4 vectors; B: 128 rows x 4 vectors
+    {
+      const int r = tid >> 2, c = (tid & 3) * 8;
+      const int row = srow[r];
+      const bool ok = row >= 0 && k0 + c < K;
+      rg_cp_async16(&As[buf][r][c], a + (ok ? (size_t)row * g.a_stride + k0 + c : 0), ok);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int idx = tid + i * MM_THREADS;
+      const int r = idx >> 2, c = (idx & 3) * 8;
+      const bool ok = n0 + r < N && k0 + c < K;
+      rg_cp_async16(&Bs[buf][r][c], w + (ok ? (size_t)(n0 + r) * K + k0 + c : 0), ok);
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+
+  load_tiles(0, 0);
+  int buf = 0;
+  for (int k0 = 0; k0 < K; k0 += MM_BK, buf ^= 1) {
+    if (k0 + MM_BK < K) {
+      load_tiles(buf ^ 1, k0 + MM_BK);
+      asm volatile("cp.async.wait_group 1;\n" ::);
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < MM_BK / 16; ++kk) {
+      uint32_t af[2][4];
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi)
+        rg_ldmatrix_x4(af[mi], &As[buf][wm + mi * 16 + (lane & 15)][kk * 16 + ((lane >> 4) << 3)]);
+#pragma unroll
+      for (int nb = 0; nb < 4; nb += 2) {
+        uint32_t b[4];
+        rg_ldmatrix_x4(b, &Bs[buf][wn + nb * 8 + (lane & 7) + ((lane >> 4) << 3)][kk * 16 + (((lane >> 3) & 1) << 3)]);
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi) {
+          rg_mma_bf16(acc[mi][nb], af[mi], b[0], b[1]);
+          rg_mma_bf16(acc[mi][nb + 1], af[mi], b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();  // all warps are done with this buffer before it is filled again
+  }
+  TO* out = (TO*)g.out + (long long)batch * g.out_batch_cols;
+#pragma unroll
+  for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      const int lr = wm + mi * 16 + gq + rr * 8;
+      const int r = m0 + lr;
+      if (r >= m_end) continue;
+      const float sc = sscale[lr];
+#pragma unroll
+      for (int nb = 0; nb < 4; ++nb)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int n = n0 + wn + nb * 8 + t4 * 2 + e;
+          if (n < N) out[(size_t)r * g.out_stride + n] = Num<TO>::from_float(acc[mi][nb][rr * 2 + e] * sc);
+        }
+    }
+}
+
+// rows_gemv: few rows per tile (single tokens). A warp streams two weight rows at a time in
+// 16-byte pieces and multiplies them with up to 8 rows of the tile; the rows come from L1. The
+// lanes' partial sums are added in a fixed order, so a row's result does not depend on the batch.
+constexpr int GV_WARPS = 8, GV_ROWS = 8, GV_COLS = 2 * GV_WARPS * 2;  // columns per block
+
+template <typename TO>
+__global__ void __launch_bounds__(GV_WARPS * 32) rows_gemv_kernel(const RowsGemm g) {
+  __shared__ int srow[BM];
+  __shared__ float sscale[BM];
+  const int tid = threadIdx.x;
+  int batch, m0, m_end;
+  if (!rows_of_block(g, batch, m0, m_end)) return;
+  if (tid < BM) {
+    const int r = m0 + tid;
+    int row = -1;
+    float sc = 1.f;
+    if (r < m_end) {
+      const int idx = g.a_rows ? g.a_rows[r] : r;
+      row = g.a_rows ? idx / g.a_div : r;
+      if (g.a_scale) sc = g.a_scale[idx];
+    }
+    srow[tid] = row;
+    sscale[tid] = sc;
+  }
+  __syncthreads();
+  const int N = g.N, K = g.K, rows = m_end - m0;
+  const bf16* a = (const bf16*)g.a + g.a_col0 + (long long)batch * g.a_batch_cols;
+  const bf16* w = (const bf16*)g.w + (long long)batch * g.w_batch_stride;
+  TO* out = (TO*)g.out + (long long)batch * g.out_batch_cols;
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int pass = 0; pass < 2; ++pass) {
+    const int n = blockIdx.x * GV_COLS + (pass * GV_WARPS + warp) * 2;
+    if (n >= N) continue;
+    const bool two = n + 1 < N;
+    const bf16* w0 = w + (size_t)n * K;
+    const bf16* w1 = w + (size_t)(two ? n + 1 : n) * K;
+    for (int r0 = 0; r0 < rows; r0 += GV_ROWS) {
+      const bf16* ar[GV_ROWS];
+#pragma unroll
+      for (int r = 0; r < GV_ROWS; ++r) ar[r] = a + (size_t)srow[min(r0 + r, rows - 1)] * g.a_stride;
+      float acc0[GV_ROWS], acc1[GV_ROWS];
+#pragma unroll
+      for (int r = 0; r < GV_ROWS; ++r) acc0[r] = acc1[r] = 0.f;
+      for (int k = lane * 8; k < K; k += 32 * 8) {
+        const Vec16<bf16> v0 = load16(w0 + k), v1 = load16(w1 + k);
+        float f0[8], f1[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          f0[e] = __bfloat162float(v0.v[e]);
+          f1[e] = __bfloat162float(v1.v[e]);
+        }
+#pragma unroll
+        for (int r = 0; r < GV_ROWS; ++r) {
+          const Vec16<bf16> av = load16(ar[r] + k);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float x = __bfloat162float(av.v[e]);
+            acc0[r] = fmaf(x, f0[e], acc0[r]);
+            acc1[r] = fmaf(x, f1[e], acc1[r]);
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < GV_ROWS; ++r) {
+        const float s0 = warp_sum(acc0[r]), s1 = warp_sum(acc1[r]);
+        if (lane == 0 && r0 + r < rows) {
+          const float sc = sscale[r0 + r];
+          TO* o = out + (size_t)(m0 + r0 + r) * g.out_stride + n;
+          o[0] = Num<TO>::from_float(s0 * sc);
+          if (two) o[1] = Num<TO>::from_float(s1 * sc);
+        }
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------ routing
 // One warp per token. scores = sigmoid(router . h) in float32; the `top` largest (the lower index
 // on a tie) with their scores; row E of the router, if there is one, is the shared expert's gate.
@@ -353,9 +574,28 @@ extern "C" int lse_latent_write(const void* proj, int in_dtype, long long stride
   return LSE_CHECK_LAUNCH();
 }
 
+// kind: 0 = CUDA cores (any operands), 1 = mma.sync tiles, 2 = few rows per tile (1 and 2: bfloat16
+// operands of whole 16-byte vectors; they multiply the result by a_scale instead of the input)
+static bool vectors_ok(const RowsGemm& g) {
+  return g.K % 8 == 0 && g.a_stride % 8 == 0 && g.a_col0 % 8 == 0 && g.a_batch_cols % 8 == 0 &&
+         reinterpret_cast<uintptr_t>(g.a) % 16 == 0 && reinterpret_cast<uintptr_t>(g.w) % 16 == 0;
+}
+
 static int launch_rows_gemm(const RowsGemm& g, int a_dtype, int w_dtype, int out_dtype, dim3 grid,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, int kind = 0) {
   if (grid.y > 65535 || grid.z > 65535) return LSE_BAD_ARGUMENT;
+  if (kind != 0 && a_dtype == LSE_BF16 && w_dtype == LSE_BF16 && vectors_ok(g)) {
+    if (kind == 1) {
+      grid.x = (g.N + MM_BN - 1) / MM_BN;
+      if (out_dtype == LSE_F32) rows_gemm_mma_kernel<float><<<grid, MM_THREADS, 0, stream>>>(g);
+      else rows_gemm_mma_kernel<bf16><<<grid, MM_THREADS, 0, stream>>>(g);
+    } else {
+      grid.x = (g.N + GV_COLS - 1) / GV_COLS;
+      if (out_dtype == LSE_F32) rows_gemv_kernel<float><<<grid, GV_WARPS * 32, 0, stream>>>(g);
+      else rows_gemv_kernel<bf16><<<grid, GV_WARPS * 32, 0, stream>>>(g);
+    }
+    return LSE_CHECK_LAUNCH();
+  }
 #define LSE_RG(TA, TW, TO) rows_gemm_kernel<TA, TW, TO><<<grid, 256, 0, stream>>>(g)
   if (a_dtype == LSE_F32 && w_dtype == LSE_F32 && out_dtype == LSE_F32) LSE_RG(float, float, float);
   else if (a_dtype == LSE_F32 && w_dtype == LSE_BF16 && out_dtype == LSE_BF16) LSE_RG(float, bf16, bf16);
@@ -369,7 +609,7 @@ static int launch_rows_gemm(const RowsGemm& g, int a_dtype, int w_dtype, int out
 
 extern "C" int lse_head_linear(const void* a, int a_dtype, long long a_stride, long long a_col0,
                                const void* w, int w_dtype, void* out, int out_dtype, int T, int H,
-                               int N, int K, cudaStream_t stream) {
+                               int N, int K, int kind, cudaStream_t stream) {
   if (T <= 0 || H <= 0 || N <= 0) return LSE_OK;
   if (K <= 0) return LSE_BAD_ARGUMENT;
   RowsGemm g = {};
@@ -377,7 +617,8 @@ extern "C" int lse_head_linear(const void* a, int a_dtype, long long a_stride, l
   g.w = w; g.w_batch_stride = (long long)N * K;
   g.out = out; g.out_stride = (long long)H * N; g.out_batch_cols = N;
   g.T = T; g.N = N; g.K = K;
-  return launch_rows_gemm(g, a_dtype, w_dtype, out_dtype, dim3((N + BN - 1) / BN, (T + BM - 1) / BM, H), stream);
+  return launch_rows_gemm(g, a_dtype, w_dtype, out_dtype, dim3((N + BN - 1) / BN, (T + BM - 1) / BM, H), stream,
+                          kind);
 }
 
 extern "C" int lse_moe_tile_rows(void) { return BM; }
@@ -386,7 +627,7 @@ extern "C" int lse_expert_linear(const void* a, int a_dtype, long long a_stride,
                                  int a_div, const float* a_scale, const void* w, int w_dtype,
                                  float* out, int rows, int N, int K, const int* offsets,
                                  const int* tile_batch, const int* tile_row0, const int* num_tiles,
-                                 int max_tiles, cudaStream_t stream) {
+                                 int max_tiles, int kind, cudaStream_t stream) {
   if (rows <= 0 || N <= 0 || max_tiles <= 0) return LSE_OK;
   if (K <= 0 || a_div <= 0 || !offsets || !tile_batch || !tile_row0 || !num_tiles) return LSE_BAD_ARGUMENT;
   RowsGemm g = {};
@@ -395,7 +636,7 @@ extern "C" int lse_expert_linear(const void* a, int a_dtype, long long a_stride,
   g.out = out; g.out_stride = N;
   g.tile_batch = tile_batch; g.tile_row0 = tile_row0; g.offsets = offsets; g.num_tiles = num_tiles;
   g.T = rows; g.N = N; g.K = K;
-  return launch_rows_gemm(g, a_dtype, w_dtype, LSE_F32, dim3((N + BN - 1) / BN, max_tiles, 1), stream);
+  return launch_rows_gemm(g, a_dtype, w_dtype, LSE_F32, dim3((N + BN - 1) / BN, max_tiles, 1), stream, kind);
 }
 
 extern "C" int lse_moe_route(const void* h, int h_dtype, const float* router, int T, int W, int E,

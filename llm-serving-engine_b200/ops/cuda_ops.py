@@ -459,11 +459,20 @@ class CudaOps:
                               block_tables)
         self.launches += 1
 
-    def head_linear(self, a, col0, w, out_dtype):
+    def _rows_kernel(self, a, w, rows: int, few: int) -> int:
+        """Which kernel serves a product over gathered rows: 0 the CUDA cores (float32, or rows
+        that are no whole 16-byte vectors), 2 the weight-streaming kernel for at most ``few`` rows,
+        1 mma.sync tiles."""
+        if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+            return 0
+        return 2 if rows <= few else 1
+
+    def head_linear(self, a, col0, w, out_dtype, kind=None):
         """A product per head: ``out[t, h] = w[h] @ a[t, col0 + h*K : col0 + (h+1)*K]`` for ``w``
-        ``[H, N, K]``; returns ``[T, H*N]``."""
+        ``[H, N, K]``; returns ``[T, H*N]``. ``kind`` forces a kernel (tests compare them)."""
         out = torch.empty(a.shape[0], w.shape[0] * w.shape[1], dtype=out_dtype, device=a.device)
-        self.ext.head_linear(a, int(col0), w, out)
+        kind = self._rows_kernel(a, w, a.shape[0], self.skinny_max_rows) if kind is None else kind
+        self.ext.head_linear(a, int(col0), w, out, int(kind))
         self.launches += 1
         return out
 
@@ -489,11 +498,13 @@ class CudaOps:
         self.launches += 1
         return work
 
-    def expert_linear(self, a, w, work, n, top=0, wts=None):
+    def expert_linear(self, a, w, work, n, top=0, wts=None, kind=None):
         """float32 ``[n, N]``: sorted row r is ``w[its expert] @ a-row``. With ``top`` the a-row is
         gathered, ``a[choice // top] * wts[choice]``; without, ``a`` is already in sorted order."""
         out = torch.empty(n, w.shape[1], dtype=torch.float32, device=a.device)
-        self.ext.expert_linear(a, w, out, work, int(n), int(top), wts)
+        # up to 128 choices over all experts: few rows per expert, the weights are the traffic
+        kind = self._rows_kernel(a, w, n, 128) if kind is None else kind
+        self.ext.expert_linear(a, w, out, work, int(n), int(top), wts, int(kind))
         self.launches += 1
         return out
 

@@ -112,7 +112,10 @@ class LatentAttention(Mixer):
     def forward(self, h, step, cache, residual=None, may_defer=False):
         s, ops = self.spec, self.ops
         tables = step.block_tables[cache.group]
-        proj = ops.linear(h, self.in_weight, None, out_dtype=torch.float32)  # q | latent, unrounded
+        # q | latent: unrounded where the kernel set's few-rows product hands on its float32 sums,
+        # in the compute dtype (the library's product rounds once) for many rows
+        few = h.shape[0] <= getattr(ops, "skinny_max_rows", 0)
+        proj = ops.linear(h, self.in_weight, None, out_dtype=torch.float32 if few else self.env.dtype)
         if s.own_latent:
             if not cache.writes:
                 raise RuntimeError("a latent-attention layer with its own latent must fill its cache layer")

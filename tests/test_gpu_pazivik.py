@@ -121,15 +121,18 @@ def test_latent_write_norms_and_finds_the_page(ops, dtype, R, page_tokens):
 @pytest.mark.parametrize("dtypes", [(torch.float32, torch.float32, torch.float32),
                                     (torch.float32, torch.bfloat16, torch.bfloat16),
                                     (torch.bfloat16, torch.bfloat16, torch.bfloat16)])
-@pytest.mark.parametrize("T,H,N,K", [(1, 1, 16, 8), (5, 3, 48, 20), (70, 2, 33, 65), (130, 4, 128, 64)])
+@pytest.mark.parametrize("T,H,N,K", [(1, 1, 16, 8), (5, 3, 48, 20), (70, 2, 33, 65), (130, 4, 128, 64), (200, 3, 136, 72)])
 def test_head_linear(ops, dtypes, T, H, N, K):
+    """Every kernel that serves the shape (CUDA cores; for bfloat16 rows of whole 16-byte vectors
+    also the tensor-core tiles and the weight-streaming kernel) against the plain product."""
     ta, tw, to = dtypes
     col0 = 8
-    a = rnd(T, col0 + H * K + 5, seed=T).to(ta)
+    a = rnd(T, col0 + H * K + (5 if K % 8 else 16), seed=T).to(ta)
     w = rnd(H, N, K, seed=K).to(tw)
-    got = ops.head_linear(a.cuda(), col0, w.cuda(), to)
     ref = torch.einsum("thk,hnk->thn", a[:, col0 : col0 + H * K].to(F).view(T, H, K), w.to(F)).reshape(T, H * N)
-    close(got, ref, 1e-5 if to == torch.float32 else 6e-3)
+    for kind in (None, 0, 1, 2):
+        got = ops.head_linear(a.cuda(), col0, w.cuda(), to, kind=kind)
+        close(got, ref, 1e-5 if to == torch.float32 else 6e-3, f"kernel {kind}")
 
 
 # ----------------------------------------------------------------------------- attention with sinks
@@ -232,6 +235,11 @@ def test_routed_experts_against_the_plain_sum(ops, dtype, T, W, E, top, ff, shar
     g = ops.expert_linear(h.cuda(), gu.cuda(), work, n, top=top, wts=wts)
     a = ops.silu_mul(g, out_dtype=dtype, activation="silu")
     y = ops.expert_linear(a, down.cuda(), work, n)
+    for kind in (0, 1, 2):  # the kernels give the same products
+        close(ops.expert_linear(h.cuda(), gu.cuda(), work, n, top=top, wts=wts, kind=kind), g.double().cpu(),
+              1e-5 if dtype == torch.float32 else 2e-3, f"gate|up, kernel {kind}")
+        close(ops.expert_linear(a, down.cuda(), work, n, kind=kind), y.double().cpu(),
+              1e-5 if dtype == torch.float32 else 2e-3, f"down, kernel {kind}")
     x = rnd(T, W, seed=5)
     into = x.clone().cuda()
     assert ops.moe_combine(y, work, E, top, None if not shared else shared_out.cuda(), gate, into) is None
