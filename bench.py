@@ -19,7 +19,8 @@ and a float32 replay of one 8192-token sequence against the plain implementation
 reference's own harness (src/llmserve/bench/run.py:96,124-176): fixed output lengths, greedy, a
 warm-up run that is thrown away, one JSON line with the environment.
 
-``--workload designs`` puts four Gubotar layers (parallel, retention, retention, parallel) beside
+``--workload designs`` (``--arms llama,gubotar,pazivik``) puts four Pazivik layers (latent attention
+with a window; dense and routed feed-forwards) and four Gubotar layers (parallel, retention, retention, parallel) beside
 four Llama layers of the same width, feed-forward and head sizes, at SmolLM2-360M and -1.7B layer
 sizes: a 2048-token prompt in one step, with its device time by kernel, and decode steps at batch
 1, 8 and 64 behind 2048-token prompts.
@@ -183,7 +184,7 @@ def graph_against_eager(engine) -> float:
     return float((captured - eager).abs().max())
 
 
-def measure_decode(engine, batch, steps, warmup, seed, check=False):
+def measure_decode(engine, batch, steps, warmup, seed, check=False, kernels=False):
     """Device and end-to-end ms per step, launches and bytes per step, contexts of the requests."""
     import torch
 
@@ -215,10 +216,11 @@ def measure_decode(engine, batch, steps, warmup, seed, check=False):
     ctx_sum = sum(s.num_tokens for s in engine.scheduler.running)
     ctx_max = max(s.num_tokens for s in engine.scheduler.running)
     diff = graph_against_eager(engine) if check else None
+    by_kernel = kernel_profile(g.graph.replay) if kernels else None  # device time of a replayed step by kernel
     for i in ids:
         engine.abort_request(i)
     return dict(dev_ms=dev_ms, e2e_ms=e2e_ms, launches=g.launches, h2d=h2d, d2h=d2h, ctx=ctx_max,
-                ctx_sum=ctx_sum, graph_vs_eager=diff)
+                ctx_sum=ctx_sum, graph_vs_eager=diff, kernels_us=by_kernel)
 
 
 def step_timeline(engine, batch, seed) -> dict:
@@ -585,6 +587,24 @@ def gubotar_layers(width, heads, kv_heads, head_dim, ff, chunk=512, state_dim=12
     return [par, ret, ret, par]
 
 
+def pazivik_layers(width, heads, head_dim, ff, rank=128, window=1024, experts=8, top=2):
+    """Four Pazivik layers at a Llama layer's sizes: the Llama layer's heads on a latent of ``rank``
+    dims with a window; a dense feed-forward of the Llama layer's size in layers 0 and 2; in layers
+    1 and 3 (which read the latent rows of the layer before them) ``experts`` experts of a quarter
+    of that size, ``top`` per token, beside a shared one."""
+    def layer(mlp, kv_from=None):
+        m = {"heads": heads, "dim": head_dim, "vdim": head_dim, "kv_rank": rank, "scale": head_dim ** -0.5,
+             "mask": {"size": window}}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return {"type": "latent_attention", "mixer": m, "mlp": mlp}
+
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff // 4},
+           "shared": {"ff": ff // 4}}
+    return [layer(dense), layer(moe, 0), layer(dense), layer(moe, 2)]
+
+
 def kernel_profile(fn, reps=3) -> dict:
     """Device time of ``fn()`` by kernel, from the framework's profiler: microseconds per call."""
     import collections
@@ -624,7 +644,10 @@ def designs_main(args) -> int:
             "llama": (f"random:{alias}", {"num_hidden_layers": 4}),
             "gubotar": ("random:gubotar-2048", {"width": w, "vocab": ll["vocab_size"],
                                                  "layers": gubotar_layers(w, heads, kv, hd, ff, state_dim=hd if w < 2048 else 128)}),
+            "pazivik": ("random:pazivik-2048", {"width": w, "vocab": ll["vocab_size"],
+                                                 "layers": pazivik_layers(w, heads, hd, ff)}),
         }
+        arms = {k: v for k, v in arms.items() if k in args.arms.split(",")}
         row = {"sizes": f"{alias}: width {w}, ff {ff}, {heads} heads of {hd}, 4 layers"}
         for name, (model, over) in arms.items():
             page = args.page_tokens
@@ -647,7 +670,9 @@ def designs_main(args) -> int:
 
             r["prefill_kernels_us"] = kernel_profile(one_prefill)
             for b in (1, 8, 64):
-                d = measure_decode(engine, b, args.steps, args.warmup, seed=20 + b)
+                d = measure_decode(engine, b, args.steps, args.warmup, seed=20 + b, kernels=b == 8)
+                if d["kernels_us"]:
+                    r[f"decode_b{b}_kernels_us"] = d["kernels_us"]
                 r[f"decode_b{b}_ms"] = round(d["dev_ms"], 4)
                 r[f"decode_b{b}_tok_s"] = round(b * 1e3 / d["dev_ms"])
                 r[f"decode_b{b}_launches"] = d["launches"]
@@ -772,6 +797,8 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode", "continuous", "long", "designs"])
+    ap.add_argument("--arms", default="llama,gubotar,pazivik",
+                    help="--workload designs: which architectures run side by side")
     ap.add_argument("--model", default="smollm2-1.7b")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0 = all)")

@@ -508,22 +508,27 @@ void moe_route(const Tensor& h, const Tensor& router, int64_t E, int64_t top, Te
 
 // work: int32 [>= (E + 1) + 2 n + 2 max_tiles + 1] holding offsets | perm | pos_of | tile_batch |
 // tile_row0 | num_tiles, max_tiles = n / tile_rows + E.
-int64_t moe_max_tiles(int64_t n, int64_t E) { return n / lse_moe_tile_rows() + E; }
+int64_t moe_max_tiles(int64_t n, int64_t E, int64_t tile_rows) { return n / tile_rows + E; }
+int64_t moe_tile_rows(int64_t kind) { return kind == 3 ? lse_expert_linear_tc_tile_rows() : lse_moe_tile_rows(); }
 
-void moe_sort(const Tensor& idx, int64_t E, Tensor& work) {
+void moe_sort(const Tensor& idx, int64_t E, Tensor& work, int64_t tile_rows) {
   check_i32(idx, "idx");
   check_i32(work, "work");
-  const int64_t n = idx.numel(), mt = moe_max_tiles(n, E);
+  TORCH_CHECK(tile_rows > 0, "moe_sort: tile_rows must be positive");
+  const int64_t n = idx.numel(), mt = moe_max_tiles(n, E, tile_rows);
   TORCH_CHECK(work.numel() >= E + 1 + 2 * n + 2 * mt + 1, "moe_sort: work too small");
   int* p = work.data_ptr<int>();
-  done(lse_moe_sort(idx.data_ptr<int>(), (int)n, (int)E, p, p + E + 1, p + E + 1 + n, p + E + 1 + 2 * n,
-                    p + E + 1 + 2 * n + mt, p + E + 1 + 2 * n + 2 * mt, stream()),
+  done(lse_moe_sort(idx.data_ptr<int>(), (int)n, (int)E, (int)tile_rows, p, p + E + 1, p + E + 1 + n,
+                    p + E + 1 + 2 * n, p + E + 1 + 2 * n + mt, p + E + 1 + 2 * n + 2 * mt, stream()),
        "moe_sort");
 }
 
-// out[r] = w[expert of sorted row r] . a-row(r); gather: a-row(r) = a[choice / top] * wts[choice]
+// out[r] = w[expert of sorted row r] . a-row(r); gather: a-row(r) = a[choice / top] * wts[choice].
+// kind 0..2: see lse_expert_linear (tiles of lse_moe_tile_rows() rows); kind 3: tcgen05 tensor cores
+// (bfloat16, K a multiple of 8, tiles of lse_expert_linear_tc_tile_rows() rows; with top the rows are
+// first gathered into `gathered` [n, K]).
 void expert_linear(const Tensor& a, const Tensor& w, Tensor& out, const Tensor& work, int64_t n, int64_t top,
-                   const OptTensor& wts, int64_t kind) {
+                   const OptTensor& wts, int64_t kind, const OptTensor& gathered) {
   check_cuda(a, "a");
   check_cuda(w, "w");
   check_f32(out, "out");
@@ -531,7 +536,7 @@ void expert_linear(const Tensor& a, const Tensor& w, Tensor& out, const Tensor& 
   TORCH_CHECK(a.dim() == 2 && w.dim() == 3 && out.dim() == 2 && w.size(2) == a.size(1) && out.size(0) == n &&
                   out.size(1) == w.size(1),
               "expert_linear: need a [rows, K], w [E, N, K], out [n, N]");
-  const int64_t E = w.size(0), mt = moe_max_tiles(n, E);
+  const int64_t E = w.size(0), mt = moe_max_tiles(n, E, moe_tile_rows(kind));
   TORCH_CHECK(work.numel() >= E + 1 + 2 * n + 2 * mt + 1, "expert_linear: work too small");
   const bool gather = top > 0;
   TORCH_CHECK(gather ? a.size(0) * top == n : a.size(0) == n, "expert_linear: rows of a disagree with n");
@@ -542,10 +547,30 @@ void expert_linear(const Tensor& a, const Tensor& w, Tensor& out, const Tensor& 
     sc = wts->data_ptr<float>();
   }
   const int* p = work.data_ptr<int>();
-  done(lse_expert_linear(a.data_ptr(), out_code(a, "a"), a.size(1), gather ? p + E + 1 : nullptr,
+  const int *perm = p + E + 1, *tile_batch = p + E + 1 + 2 * n, *tile_row0 = tile_batch + mt, *num_tiles = tile_row0 + mt;
+  if (kind == 3) {
+    TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16 && a.size(1) % 8 == 0,
+                "expert_linear: the tcgen05 kernel takes bfloat16 rows of a multiple of 8 elements");
+    const void* rows = a.data_ptr();
+    if (gather) {
+      TORCH_CHECK(gathered.has_value(), "expert_linear: the tcgen05 kernel needs room for the gathered rows");
+      check_cuda(*gathered, "gathered");
+      TORCH_CHECK(gathered->scalar_type() == torch::kBFloat16 && gathered->numel() >= n * a.size(1),
+                  "expert_linear: gathered must be bfloat16 [n, K]");
+      done(lse_moe_gather_rows(a.data_ptr(), perm, (int)top, gathered->data_ptr(), (int)n, (int)a.size(1), stream()),
+           "expert_linear (gather)");
+      rows = gathered->data_ptr();
+    }
+    done(lse_expert_linear_tc(rows, w.data_ptr(), out.data_ptr<float>(), (int)n, (int)E, (int)w.size(1),
+                              (int)w.size(2), sc, perm, p, tile_batch, tile_row0, num_tiles, (int)mt, error_flag(),
+                              stream()),
+         "expert_linear (tcgen05)");
+    return;
+  }
+  done(lse_expert_linear(a.data_ptr(), out_code(a, "a"), a.size(1), gather ? perm : nullptr,
                          gather ? (int)top : 1, sc, w.data_ptr(), out_code(w, "w"), out.data_ptr<float>(),
-                         (int)n, (int)w.size(1), (int)w.size(2), p, p + E + 1 + 2 * n, p + E + 1 + 2 * n + mt,
-                         p + E + 1 + 2 * n + 2 * mt, (int)mt, (int)kind, stream()),
+                         (int)n, (int)w.size(1), (int)w.size(2), p, tile_batch, tile_row0, num_tiles, (int)mt,
+                         (int)kind, stream()),
        "expert_linear");
 }
 
@@ -977,6 +1002,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("head_linear", &head_linear);
   m.def("moe_route", &moe_route);
   m.def("moe_max_tiles", &moe_max_tiles);
+  m.def("moe_tile_rows", &moe_tile_rows);
   m.def("moe_sort", &moe_sort);
   m.def("expert_linear", &expert_linear);
   m.def("moe_combine", &moe_combine);

@@ -204,7 +204,8 @@ int lse_head_linear(const void* a, int a_dtype, long long a_stride, long long a_
 //     first, the lower index on a tie) and their scores; with has_gate, gate[t] = sigmoid(router[E] . h).
 //   lse_moe_sort: the n = T * top choices sorted by expert: offsets [E + 1], perm [n] (sorted row ->
 //     choice), pos_of [n] (choice -> sorted row), and tiles of at most lse_moe_tile_rows() rows of one
-//     expert each (tile_batch, tile_row0: room for n / tile_rows + E entries; num_tiles [1]).
+//     expert each (tile_batch, tile_row0: room for n / tile_rows + E entries; num_tiles [1]);
+//     tile_rows is lse_moe_tile_rows() for lse_expert_linear.
 //   lse_expert_linear: out[r, :] = w[expert of r] . arow(r) for every sorted row r, float32 out
 //     [rows, N]; arow(r) = a[a_rows[r] / a_div] * a_scale[a_rows[r]] (a_rows null: a[r], unscaled);
 //     w [E, N, K]. Launched for max_tiles tiles; tiles beyond *num_tiles do nothing. kind as above
@@ -213,8 +214,19 @@ int lse_head_linear(const void* a, int a_dtype, long long a_stride, long long a_
 int lse_moe_tile_rows(void);
 int lse_moe_route(const void* h, int h_dtype, const float* router, int T, int W, int E, int has_gate,
                   int top, int* idx, float* wts, float* gate, cudaStream_t stream);
-int lse_moe_sort(const int* idx, int n, int E, int* offsets, int* perm, int* pos_of, int* tile_batch,
-                 int* tile_row0, int* num_tiles, cudaStream_t stream);
+int lse_moe_sort(const int* idx, int n, int E, int tile_rows, int* offsets, int* perm, int* pos_of,
+                 int* tile_batch, int* tile_row0, int* num_tiles, cudaStream_t stream);
+// out[r] = a[perm[r] / top] for the n sorted rows (bfloat16, K a multiple of 8)
+int lse_moe_gather_rows(const void* a, const int* perm, int top, void* out, int n, int K,
+                        cudaStream_t stream);
+// lse_expert_linear for bfloat16 rows that already lie sorted (a [rows, K], K a multiple of 8), on
+// tcgen05 tensor cores (grouped_gemm_tc.cu); the tiles must hold lse_expert_linear_tc_tile_rows()
+// rows. out[r] is multiplied by scale[perm[r]] if scale is given.
+int lse_expert_linear_tc_tile_rows(void);
+int lse_expert_linear_tc(const void* a, const void* w, float* out, int rows, int E, int N, int K,
+                         const float* scale, const int* perm, const int* offsets,
+                         const int* tile_batch, const int* tile_row0, const int* num_tiles,
+                         int max_tiles, int* error_flag, cudaStream_t stream);
 int lse_expert_linear(const void* a, int a_dtype, long long a_stride, const int* a_rows, int a_div,
                       const float* a_scale, const void* w, int w_dtype, float* out, int rows, int N,
                       int K, const int* offsets, const int* tile_batch, const int* tile_row0,

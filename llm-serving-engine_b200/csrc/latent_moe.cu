@@ -23,6 +23,8 @@ hashed_pair_add_kernel(float* __restrict__ x, const T* __restrict__ table, int* 
                        const int* __restrict__ token_seq, const int* __restrict__ cu_q,
                        const int* __restrict__ slots, int W, long long buckets, long long mul_prev,
                        long long mul_cur) {
+  pdl_trigger();
+  pdl_wait();  // everything below reads what kernels before this one wrote
   const int t = blockIdx.x;
   const int seq = token_seq[t];
   const int first = cu_q[seq];
@@ -43,6 +45,8 @@ hashed_pair_add_kernel(float* __restrict__ x, const T* __restrict__ table, int* 
 __global__ void __launch_bounds__(128)
 sinusoid_add_kernel(float* __restrict__ x, const int* __restrict__ positions,
                     const float* __restrict__ freq, int W) {
+  pdl_trigger();
+  pdl_wait();  // everything below reads what kernels before this one wrote
   const int t = blockIdx.x;
   const float p = (float)positions[t];
   float* dst = x + (size_t)t * W;
@@ -59,6 +63,8 @@ latent_write_kernel(const TIn* __restrict__ proj, long long stride, int col0, in
                     const float* __restrict__ weight, float eps, T* __restrict__ pages,
                     const int* __restrict__ positions, const int* __restrict__ token_seq,
                     const int* __restrict__ block_tables, int table_stride, int page_tokens) {
+  pdl_trigger();
+  pdl_wait();  // everything below reads what kernels before this one wrote
   __shared__ float red[32];
   const int t = blockIdx.x;
   const TIn* src = proj + (size_t)t * stride + col0;
@@ -100,6 +106,8 @@ struct RowsGemm {
 
 template <typename TA, typename TW, typename TO>
 __global__ void __launch_bounds__(256) rows_gemm_kernel(const RowsGemm g) {
+  pdl_trigger();
+  pdl_wait();  // everything below reads what kernels before this one wrote
   __shared__ float as[BK][BM + 4];
   __shared__ float ws[BK][BN + 4];
   __shared__ int srow[BM];
@@ -235,6 +243,8 @@ __device__ __forceinline__ bool rows_of_block(const RowsGemm& g, int& batch, int
 
 template <typename TO>
 __global__ void __launch_bounds__(MM_THREADS) rows_gemm_mma_kernel(const RowsGemm g) {
+  pdl_trigger();
+  pdl_wait();  // everything below reads what kernels before this one wrote
   __shared__ __align__(16) bf16 As[2][BM][MM_LD];
   __shared__ __align__(16) bf16 Bs[2][MM_BN][MM_LD];
   __shared__ int srow[BM];
@@ -334,13 +344,57 @@ __global__ void __launch_bounds__(MM_THREADS) rows_gemm_mma_kernel(const RowsGem
     }
 }
 
-// rows_gemv: few rows per tile (single tokens). A warp streams two weight rows at a time in
-// 16-byte pieces and multiplies them with up to 8 rows of the tile; the rows come from L1. The
-// lanes' partial sums are added in a fixed order, so a row's result does not depend on the batch.
-constexpr int GV_WARPS = 8, GV_ROWS = 8, GV_COLS = 2 * GV_WARPS * 2;  // columns per block
+// rows_gemv: few rows per tile (single tokens). A warp streams four weight rows at a time in
+// 16-byte pieces, two steps of k in flight, and multiplies them with up to RN rows of the tile
+// (RN = 2, 4 or 8 by the tile's row count; more rows take further passes); the rows come from L1.
+// The lanes' partial sums are added in a fixed order, so a row's result does not depend on the batch.
+constexpr int GV_WARPS = 8, GV_ROWS = 8, GV_CPW = 4, GV_COLS = GV_WARPS * GV_CPW;  // columns per block
+
+template <typename TO, int RN>
+__device__ __forceinline__ void gemv_rows(const RowsGemm& g, const bf16* a, const bf16* w, TO* out,
+                                          const int* srow, const float* sscale, int m0, int r0, int rows,
+                                          int n, int lane) {
+  const int K = g.K, N = g.N;
+  const bf16* wr[GV_CPW];
+#pragma unroll
+  for (int c = 0; c < GV_CPW; ++c) wr[c] = w + (size_t)min(n + c, N - 1) * K;
+  const bf16* ar[RN];
+#pragma unroll
+  for (int r = 0; r < RN; ++r) ar[r] = a + (size_t)srow[min(r0 + r, rows - 1)] * g.a_stride;
+  float acc[GV_CPW][RN];
+#pragma unroll
+  for (int c = 0; c < GV_CPW; ++c)
+#pragma unroll
+    for (int r = 0; r < RN; ++r) acc[c][r] = 0.f;
+  for (int k = lane * 8; k < K; k += 32 * 8) {
+    Vec16<bf16> wv[GV_CPW];
+#pragma unroll
+    for (int c = 0; c < GV_CPW; ++c) wv[c] = load16(wr[c] + k);
+#pragma unroll
+    for (int r = 0; r < RN; ++r) {
+      const Vec16<bf16> av = load16(ar[r] + k);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float x = __bfloat162float(av.v[e]);
+#pragma unroll
+        for (int c = 0; c < GV_CPW; ++c) acc[c][r] = fmaf(x, __bfloat162float(wv[c].v[e]), acc[c][r]);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < RN; ++r)
+#pragma unroll
+    for (int c = 0; c < GV_CPW; ++c) {
+      const float sum = warp_sum(acc[c][r]);
+      if (lane == 0 && r0 + r < rows && n + c < N)
+        out[(size_t)(m0 + r0 + r) * g.out_stride + n + c] = Num<TO>::from_float(sum * sscale[r0 + r]);
+    }
+}
 
 template <typename TO>
 __global__ void __launch_bounds__(GV_WARPS * 32) rows_gemv_kernel(const RowsGemm g) {
+  pdl_trigger();
+  pdl_wait();  // everything below reads what kernels before this one wrote
   __shared__ int srow[BM];
   __shared__ float sscale[BM];
   const int tid = threadIdx.x;
@@ -348,7 +402,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) rows_gemv_kernel(const RowsGemm
   if (!rows_of_block(g, batch, m0, m_end)) return;
   if (tid < BM) {
     const int r = m0 + tid;
-    int row = -1;
+    int row = 0;
     float sc = 1.f;
     if (r < m_end) {
       const int idx = g.a_rows ? g.a_rows[r] : r;
@@ -359,74 +413,41 @@ __global__ void __launch_bounds__(GV_WARPS * 32) rows_gemv_kernel(const RowsGemm
     sscale[tid] = sc;
   }
   __syncthreads();
-  const int N = g.N, K = g.K, rows = m_end - m0;
+  const int rows = m_end - m0;
+  if (rows <= 0) return;
   const bf16* a = (const bf16*)g.a + g.a_col0 + (long long)batch * g.a_batch_cols;
   const bf16* w = (const bf16*)g.w + (long long)batch * g.w_batch_stride;
   TO* out = (TO*)g.out + (long long)batch * g.out_batch_cols;
   const int warp = tid >> 5, lane = tid & 31;
-  for (int pass = 0; pass < 2; ++pass) {
-    const int n = blockIdx.x * GV_COLS + (pass * GV_WARPS + warp) * 2;
-    if (n >= N) continue;
-    const bool two = n + 1 < N;
-    const bf16* w0 = w + (size_t)n * K;
-    const bf16* w1 = w + (size_t)(two ? n + 1 : n) * K;
-    for (int r0 = 0; r0 < rows; r0 += GV_ROWS) {
-      const bf16* ar[GV_ROWS];
-#pragma unroll
-      for (int r = 0; r < GV_ROWS; ++r) ar[r] = a + (size_t)srow[min(r0 + r, rows - 1)] * g.a_stride;
-      float acc0[GV_ROWS], acc1[GV_ROWS];
-#pragma unroll
-      for (int r = 0; r < GV_ROWS; ++r) acc0[r] = acc1[r] = 0.f;
-      for (int k = lane * 8; k < K; k += 32 * 8) {
-        const Vec16<bf16> v0 = load16(w0 + k), v1 = load16(w1 + k);
-        float f0[8], f1[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          f0[e] = __bfloat162float(v0.v[e]);
-          f1[e] = __bfloat162float(v1.v[e]);
-        }
-#pragma unroll
-        for (int r = 0; r < GV_ROWS; ++r) {
-          const Vec16<bf16> av = load16(ar[r] + k);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const float x = __bfloat162float(av.v[e]);
-            acc0[r] = fmaf(x, f0[e], acc0[r]);
-            acc1[r] = fmaf(x, f1[e], acc1[r]);
-          }
-        }
-      }
-#pragma unroll
-      for (int r = 0; r < GV_ROWS; ++r) {
-        const float s0 = warp_sum(acc0[r]), s1 = warp_sum(acc1[r]);
-        if (lane == 0 && r0 + r < rows) {
-          const float sc = sscale[r0 + r];
-          TO* o = out + (size_t)(m0 + r0 + r) * g.out_stride + n;
-          o[0] = Num<TO>::from_float(s0 * sc);
-          if (two) o[1] = Num<TO>::from_float(s1 * sc);
-        }
-      }
-    }
+  const int n = blockIdx.x * GV_COLS + warp * GV_CPW;
+  if (n >= g.N) return;
+  for (int r0 = 0; r0 < rows; r0 += GV_ROWS) {
+    const int left = rows - r0;
+    if (left <= 2) gemv_rows<TO, 2>(g, a, w, out, srow, sscale, m0, r0, rows, n, lane);
+    else if (left <= 4) gemv_rows<TO, 4>(g, a, w, out, srow, sscale, m0, r0, rows, n, lane);
+    else gemv_rows<TO, GV_ROWS>(g, a, w, out, srow, sscale, m0, r0, rows, n, lane);
   }
 }
 
 // ------------------------------------------------------------------------------------ routing
-// One warp per token. scores = sigmoid(router . h) in float32; the `top` largest (the lower index
-// on a tie) with their scores; row E of the router, if there is one, is the shared expert's gate.
-constexpr int ROUTE_WARPS = 4;
+// One block of eight warps per token: warp w takes the router's rows w, w + 8, ... (scores =
+// sigmoid(router . h) in float32, a row's sum in an order that depends on nothing but the width);
+// then the first warp picks the `top` largest (the lower index on a tie) with their scores. Row E
+// of the router, if there is one, is the shared expert's gate.
+constexpr int ROUTE_WARPS = 8;
 
 template <typename TH>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
-moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ router, int T, int W, int E,
+moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ router, int W, int E,
                  int has_gate, int top, int* __restrict__ idx, float* __restrict__ wts,
                  float* __restrict__ gate) {
-  extern __shared__ float sm_scores[];  // [ROUTE_WARPS][E]
+  pdl_trigger();
+  pdl_wait();  // everything below reads what kernels before this one wrote
+  extern __shared__ float s[];  // [E]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * ROUTE_WARPS + warp;
-  if (t >= T) return;
-  float* s = sm_scores + warp * E;
-  const TH* row = h + (size_t)t * W;
-  for (int e = 0; e < E + has_gate; ++e) {
+  const size_t t = blockIdx.x;
+  const TH* row = h + t * W;
+  for (int e = warp; e < E + has_gate; e += ROUTE_WARPS) {
     const float* r = router + (size_t)e * W;
     float d = 0.f;
     for (int i = lane; i < W; i += 32) d = fmaf(Num<TH>::to_float(row[i]), r[i], d);
@@ -437,7 +458,8 @@ moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ router, int
       else gate[t] = sg;
     }
   }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   for (int k = 0; k < top; ++k) {
     float best = -2.f;
     int bi = 0x7fffffff;
@@ -456,8 +478,8 @@ moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ router, int
       }
     }
     if (lane == 0) {
-      idx[(size_t)t * top + k] = bi;
-      wts[(size_t)t * top + k] = best;
+      idx[t * top + k] = bi;
+      wts[t * top + k] = best;
       s[bi] = -1.f;  // taken (a sigmoid is never negative)
     }
     __syncwarp();
@@ -466,11 +488,13 @@ moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ router, int
 
 // One block. n choices idx[i] in [0, E): offsets[e] .. offsets[e+1] are expert e's rows in the
 // sorted order, perm[r] the choice at sorted row r, pos_of[i] the sorted row of choice i, and the
-// rows as tiles of at most BM rows of one expert (tile_batch, tile_row0, num_tiles).
+// rows as tiles of at most tile_rows rows of one expert (tile_batch, tile_row0, num_tiles).
 __global__ void __launch_bounds__(1024)
-moe_sort_kernel(const int* __restrict__ idx, int n, int E, int* __restrict__ offsets,
+moe_sort_kernel(const int* __restrict__ idx, int n, int E, int tile_rows, int* __restrict__ offsets,
                 int* __restrict__ perm, int* __restrict__ pos_of, int* __restrict__ tile_batch,
                 int* __restrict__ tile_row0, int* __restrict__ num_tiles) {
+  pdl_trigger();
+  pdl_wait();  // everything below reads what kernels before this one wrote
   extern __shared__ int sm_sort[];  // counts[E], start[E + 1], tile_start[E + 1]
   int* counts = sm_sort;
   int* start = counts + E;
@@ -485,7 +509,7 @@ moe_sort_kernel(const int* __restrict__ idx, int n, int E, int* __restrict__ off
       start[e] = run;
       tstart[e] = tiles;
       run += counts[e];
-      tiles += (counts[e] + BM - 1) / BM;
+      tiles += (counts[e] + tile_rows - 1) / tile_rows;
     }
     start[E] = run;
     tstart[E] = tiles;
@@ -497,7 +521,7 @@ moe_sort_kernel(const int* __restrict__ idx, int n, int E, int* __restrict__ off
     const int nt = tstart[e + 1] - tstart[e];
     for (int k = 0; k < nt; ++k) {
       tile_batch[tstart[e] + k] = e;
-      tile_row0[tstart[e] + k] = start[e] + k * BM;
+      tile_row0[tstart[e] + k] = start[e] + k * tile_rows;
     }
     counts[e] = 0;  // now the cursor of expert e
   }
@@ -511,11 +535,26 @@ moe_sort_kernel(const int* __restrict__ idx, int n, int E, int* __restrict__ off
   }
 }
 
+// out[r] = a[perm[r] / top]: the tokens' rows in sorted order, in 16-byte pieces (K a multiple of 8)
+__global__ void __launch_bounds__(256)
+moe_gather_rows_kernel(const bf16* __restrict__ a, const int* __restrict__ perm, int top,
+                       bf16* __restrict__ out, int n, int K) {
+  pdl_trigger();
+  pdl_wait();  // everything below reads what kernels before this one wrote
+  const int per_row = K / 8;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)n * per_row) return;
+  const int r = (int)(i / per_row), c = (int)(i - (long long)r * per_row);
+  store16(out + (size_t)r * K + c * 8, load16(a + (size_t)(perm[r] / top) * K + c * 8));
+}
+
 // x[t] (or out[t]) (+)= sum_k y[pos_of[t * top + k]] + gate[t] * shared[t]
 __global__ void __launch_bounds__(128)
 moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of, int top,
                    const float* __restrict__ shared_out, const float* __restrict__ gate,
                    float* __restrict__ out, int accumulate, int W) {
+  pdl_trigger();
+  pdl_wait();  // everything below reads what kernels before this one wrote
   const int t = blockIdx.x;
   const float g = gate ? gate[t] : 0.f;
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
@@ -540,10 +579,10 @@ extern "C" int lse_hashed_pair_add(float* x, const void* table, int table_dtype,
   if (T <= 0) return LSE_OK;
   if (buckets <= 0 || W <= 0) return LSE_BAD_ARGUMENT;
   if (table_dtype == LSE_F32)
-    hashed_pair_add_kernel<float><<<T, 128, 0, stream>>>(x, (const float*)table, state, ids, positions, token_seq,
+    launch(hashed_pair_add_kernel<float>, T, 128, 0, stream, x, (const float*)table, state, ids, positions, token_seq,
                                                          cu_q, slots, W, buckets, mul_prev, mul_cur);
   else if (table_dtype == LSE_BF16)
-    hashed_pair_add_kernel<bf16><<<T, 128, 0, stream>>>(x, (const bf16*)table, state, ids, positions, token_seq,
+    launch(hashed_pair_add_kernel<bf16>, T, 128, 0, stream, x, (const bf16*)table, state, ids, positions, token_seq,
                                                         cu_q, slots, W, buckets, mul_prev, mul_cur);
   else
     return LSE_BAD_ARGUMENT;
@@ -553,7 +592,7 @@ extern "C" int lse_hashed_pair_add(float* x, const void* table, int table_dtype,
 extern "C" int lse_sinusoid_add(float* x, const int* positions, const float* freq, int T, int W,
                                 cudaStream_t stream) {
   if (T <= 0) return LSE_OK;
-  sinusoid_add_kernel<<<T, 128, 0, stream>>>(x, positions, freq, W);
+  launch(sinusoid_add_kernel, T, 128, 0, stream, x, positions, freq, W);
   return LSE_CHECK_LAUNCH();
 }
 
@@ -564,7 +603,7 @@ extern "C" int lse_latent_write(const void* proj, int in_dtype, long long stride
   if (T <= 0) return LSE_OK;
   if (R <= 0 || Rp < R || page_tokens <= 0) return LSE_BAD_ARGUMENT;
 #define LSE_LATENT(TIn, T_) \
-  latent_write_kernel<TIn, T_><<<T, 128, 0, stream>>>((const TIn*)proj, stride, col0, R, Rp, weight, eps, \
+  launch(latent_write_kernel<TIn, T_>, T, 128, 0, stream, (const TIn*)proj, stride, col0, R, Rp, weight, eps, \
       (T_*)pages, positions, token_seq, block_tables, table_stride, page_tokens)
   if (in_dtype == LSE_F32 && dtype == LSE_F32) LSE_LATENT(float, float);
   else if (in_dtype == LSE_F32 && dtype == LSE_BF16) LSE_LATENT(float, bf16);
@@ -587,16 +626,16 @@ static int launch_rows_gemm(const RowsGemm& g, int a_dtype, int w_dtype, int out
   if (kind != 0 && a_dtype == LSE_BF16 && w_dtype == LSE_BF16 && vectors_ok(g)) {
     if (kind == 1) {
       grid.x = (g.N + MM_BN - 1) / MM_BN;
-      if (out_dtype == LSE_F32) rows_gemm_mma_kernel<float><<<grid, MM_THREADS, 0, stream>>>(g);
-      else rows_gemm_mma_kernel<bf16><<<grid, MM_THREADS, 0, stream>>>(g);
+      if (out_dtype == LSE_F32) launch(rows_gemm_mma_kernel<float>, grid, MM_THREADS, 0, stream, g);
+      else launch(rows_gemm_mma_kernel<bf16>, grid, MM_THREADS, 0, stream, g);
     } else {
       grid.x = (g.N + GV_COLS - 1) / GV_COLS;
-      if (out_dtype == LSE_F32) rows_gemv_kernel<float><<<grid, GV_WARPS * 32, 0, stream>>>(g);
-      else rows_gemv_kernel<bf16><<<grid, GV_WARPS * 32, 0, stream>>>(g);
+      if (out_dtype == LSE_F32) launch(rows_gemv_kernel<float>, grid, GV_WARPS * 32, 0, stream, g);
+      else launch(rows_gemv_kernel<bf16>, grid, GV_WARPS * 32, 0, stream, g);
     }
     return LSE_CHECK_LAUNCH();
   }
-#define LSE_RG(TA, TW, TO) rows_gemm_kernel<TA, TW, TO><<<grid, 256, 0, stream>>>(g)
+#define LSE_RG(TA, TW, TO) launch(rows_gemm_kernel<TA, TW, TO>, grid, 256, 0, stream, g)
   if (a_dtype == LSE_F32 && w_dtype == LSE_F32 && out_dtype == LSE_F32) LSE_RG(float, float, float);
   else if (a_dtype == LSE_F32 && w_dtype == LSE_BF16 && out_dtype == LSE_BF16) LSE_RG(float, bf16, bf16);
   else if (a_dtype == LSE_F32 && w_dtype == LSE_BF16 && out_dtype == LSE_F32) LSE_RG(float, bf16, float);
@@ -644,25 +683,35 @@ extern "C" int lse_moe_route(const void* h, int h_dtype, const float* router, in
                              cudaStream_t stream) {
   if (T <= 0) return LSE_OK;
   if (E <= 0 || top <= 0 || top > E || E > 2048 || (has_gate && !gate)) return LSE_BAD_ARGUMENT;
-  const int blocks = (T + ROUTE_WARPS - 1) / ROUTE_WARPS;
-  const size_t smem = (size_t)ROUTE_WARPS * E * sizeof(float);
+  const size_t smem = (size_t)E * sizeof(float);
   if (h_dtype == LSE_F32)
-    moe_route_kernel<float><<<blocks, ROUTE_WARPS * 32, smem, stream>>>((const float*)h, router, T, W, E, has_gate,
-                                                                        top, idx, wts, gate);
+    launch(moe_route_kernel<float>, T, ROUTE_WARPS * 32, smem, stream, (const float*)h, router, W, E, has_gate, top,
+                                                                   idx, wts, gate);
   else if (h_dtype == LSE_BF16)
-    moe_route_kernel<bf16><<<blocks, ROUTE_WARPS * 32, smem, stream>>>((const bf16*)h, router, T, W, E, has_gate,
-                                                                       top, idx, wts, gate);
+    launch(moe_route_kernel<bf16>, T, ROUTE_WARPS * 32, smem, stream, (const bf16*)h, router, W, E, has_gate, top,
+                                                                  idx, wts, gate);
   else
     return LSE_BAD_ARGUMENT;
   return LSE_CHECK_LAUNCH();
 }
 
-extern "C" int lse_moe_sort(const int* idx, int n, int E, int* offsets, int* perm, int* pos_of,
+extern "C" int lse_moe_sort(const int* idx, int n, int E, int tile_rows, int* offsets, int* perm, int* pos_of,
                             int* tile_batch, int* tile_row0, int* num_tiles, cudaStream_t stream) {
   if (n <= 0) return LSE_OK;
-  if (E <= 0 || E > 2048) return LSE_BAD_ARGUMENT;
+  if (E <= 0 || E > 2048 || tile_rows <= 0) return LSE_BAD_ARGUMENT;
   const size_t smem = (size_t)(3 * E + 2) * sizeof(int);
-  moe_sort_kernel<<<1, 1024, smem, stream>>>(idx, n, E, offsets, perm, pos_of, tile_batch, tile_row0, num_tiles);
+  launch(moe_sort_kernel, 1, 1024, smem, stream, idx, n, E, tile_rows, offsets, perm, pos_of, tile_batch, tile_row0,
+                                             num_tiles);
+  return LSE_CHECK_LAUNCH();
+}
+
+extern "C" int lse_moe_gather_rows(const void* a, const int* perm, int top, void* out, int n, int K,
+                                   cudaStream_t stream) {
+  if (n <= 0) return LSE_OK;
+  if (K <= 0 || K % 8 || top <= 0) return LSE_BAD_ARGUMENT;
+  const long long items = (long long)n * (K / 8);
+  launch(moe_gather_rows_kernel, (unsigned)((items + 255) / 256), 256, 0, stream, (const bf16*)a, perm, top, (bf16*)out,
+                                                                              n, K);
   return LSE_CHECK_LAUNCH();
 }
 
@@ -671,6 +720,6 @@ extern "C" int lse_moe_combine(const float* y, const int* pos_of, int top, const
                                cudaStream_t stream) {
   if (T <= 0) return LSE_OK;
   if (shared_out && !gate) return LSE_BAD_ARGUMENT;
-  moe_combine_kernel<<<T, 128, 0, stream>>>(y, pos_of, top, shared_out, gate, out, accumulate, W);
+  launch(moe_combine_kernel, T, 128, 0, stream, y, pos_of, top, shared_out, gate, out, accumulate, W);
   return LSE_CHECK_LAUNCH();
 }

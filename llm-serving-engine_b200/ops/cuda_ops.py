@@ -52,6 +52,17 @@ class PendingSums:
         return None
 
 
+class MoePlan:
+    """What :meth:`CudaOps.moe_sort` leaves for the experts' products and the final sum: the int32
+    work buffer (row ranges, the sorted order and its inverse, tiles), the number of choices, the
+    number of experts and which kernel the tiles were cut for."""
+
+    __slots__ = ("work", "n", "num_experts", "kind")
+
+    def __init__(self, work, n, num_experts, kind) -> None:
+        self.work, self.n, self.num_experts, self.kind = work, n, num_experts, kind
+
+
 class DeferredProduct:
     """A few-rows product whose fixed-point sums nobody has taken yet. What ``linear`` may return
     to a caller that says ``may_defer=True`` without a tensor to add into: a kernel that reads the
@@ -488,29 +499,45 @@ class CudaOps:
         self.launches += 1
         return idx, wts, gate
 
-    def moe_sort(self, idx, num_experts):
-        """The choices sorted by expert, as row ranges and tiles for :meth:`expert_linear` (an
-        opaque int32 work buffer that :meth:`moe_combine` reads too)."""
+    def moe_sort(self, idx, num_experts, dtype, width=0, kind=None):
+        """The choices sorted by expert, as row ranges and tiles for :meth:`expert_linear`: a plan
+        that :meth:`moe_combine` reads too. ``dtype`` and ``width`` (of the experts' input) choose
+        the kernel of the products: 0 the CUDA cores (float32), 2 the weight-streaming kernel (up
+        to 128 choices: few rows per expert), 1 mma.sync tiles, 3 tcgen05 tiles (many rows of
+        whole 16-byte vectors); ``kind`` forces one."""
         n = idx.numel()
-        tiles = int(self.ext.moe_max_tiles(n, int(num_experts)))
+        if kind is None:
+            if dtype != torch.bfloat16:
+                kind = 0
+            elif n <= 128:
+                kind = 2
+            else:
+                kind = 3 if (n > 1024 and width % 8 == 0) else 1
+        tile_rows = int(self.ext.moe_tile_rows(int(kind)))
+        tiles = int(self.ext.moe_max_tiles(n, int(num_experts), tile_rows))
         work = torch.empty(num_experts + 1 + 2 * n + 2 * tiles + 1, dtype=torch.int32, device=idx.device)
-        self.ext.moe_sort(idx, int(num_experts), work)
+        self.ext.moe_sort(idx, int(num_experts), work, tile_rows)
         self.launches += 1
-        return work
+        return MoePlan(work, n, int(num_experts), int(kind))
 
-    def expert_linear(self, a, w, work, n, top=0, wts=None, kind=None):
+    def expert_linear(self, a, w, plan, top=0, wts=None):
         """float32 ``[n, N]``: sorted row r is ``w[its expert] @ a-row``. With ``top`` the a-row is
         gathered, ``a[choice // top] * wts[choice]``; without, ``a`` is already in sorted order."""
-        out = torch.empty(n, w.shape[1], dtype=torch.float32, device=a.device)
-        # up to 128 choices over all experts: few rows per expert, the weights are the traffic
-        kind = self._rows_kernel(a, w, n, 128) if kind is None else kind
-        self.ext.expert_linear(a, w, out, work, int(n), int(top), wts, int(kind))
+        out = torch.empty(plan.n, w.shape[1], dtype=torch.float32, device=a.device)
+        kind, gathered = plan.kind, None
+        if kind == 3 and (a.shape[1] % 8 or a.dtype != torch.bfloat16):
+            raise ValueError("this plan's kernel takes bfloat16 rows of a multiple of 8 elements")
+        if kind == 3 and top:
+            gathered = torch.empty(plan.n, a.shape[1], dtype=a.dtype, device=a.device)
+            self.launches += 1
+        self.ext.expert_linear(a, w, out, plan.work, plan.n, int(top), wts, kind, gathered)
         self.launches += 1
         return out
 
-    def moe_combine(self, y, work, num_experts, top, shared, gate, residual):
+    def moe_combine(self, y, plan, top, shared, gate, residual):
         """Per token the sum of its experts' rows of ``y`` (+ gate * shared): added into
         ``residual`` (returns None) or returned."""
+        work, num_experts = plan.work, plan.num_experts
         T = y.shape[0] // top
         out = residual if residual is not None else torch.empty(T, y.shape[1], dtype=torch.float32, device=y.device)
         self.ext.moe_combine(y, work, int(num_experts), int(top), shared, gate if shared is not None else None,

@@ -69,9 +69,14 @@ class RoutedExperts(FeedForward):
     def forward(self, h, step, residual=None, may_defer=False):
         s, ops = self.spec, self.ops
         idx, wts, gate = ops.moe_route(h, self.router_weight, s.num_experts, s.top, self.shared is not None)
-        work = ops.moe_sort(idx, s.num_experts)
-        gu = ops.expert_linear(h, self.gate_up_weight, work, idx.numel(), top=s.top, wts=wts)
+        plan = ops.moe_sort(idx, s.num_experts, self.env.dtype, width=_gcd8(s.hidden_size, s.expert_size))
+        gu = ops.expert_linear(h, self.gate_up_weight, plan, top=s.top, wts=wts)
         a = ops.silu_mul(gu, out_dtype=self.env.dtype, activation=s.activation)
-        y = ops.expert_linear(a, self.down_weight, work, idx.numel())
+        y = ops.expert_linear(a, self.down_weight, plan)
         shared = self.shared.forward(h, step) if self.shared is not None else None
-        return ops.moe_combine(y, work, s.num_experts, s.top, shared, gate, residual)
+        return ops.moe_combine(y, plan, s.top, shared, gate, residual)
+
+
+def _gcd8(*sizes: int) -> int:
+    """8 if every size is a multiple of 8 (rows of whole 16-byte vectors in bfloat16), else 1."""
+    return 8 if all(n % 8 == 0 for n in sizes) else 1

@@ -233,15 +233,15 @@ class PlainOps:
         val, idx = torch.topk(z[:, :num_experts], top, dim=-1)
         return idx.to(torch.int32), val, (z[:, num_experts] if has_gate else None)
 
-    def moe_sort(self, idx, num_experts):
+    def moe_sort(self, idx, num_experts, dtype, width=0, kind=None):
         return idx  # the plain products below walk the choices as they are
 
-    def expert_linear(self, a, w, work, n, top=0, wts=None):
-        idx = work.reshape(-1).long()
+    def expert_linear(self, a, w, plan, top=0, wts=None):
+        idx = plan.reshape(-1).long()
         rows = a.float() if top == 0 else a.float().repeat_interleave(top, 0) * wts.reshape(-1, 1)
         return torch.einsum("rk,rnk->rn", rows, w.float()[idx])
 
-    def moe_combine(self, y, work, num_experts, top, shared, gate, residual):
+    def moe_combine(self, y, plan, top, shared, gate, residual):
         out = y.view(-1, top, y.shape[1]).sum(1)
         if shared is not None:
             out = out + gate[:, None] * shared.float()

@@ -209,7 +209,7 @@ def test_a_key_at_the_windows_edge(ops, dtype, n_rows, splits, edge):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("T,W,E,top,ff,shared", [(1, 70, 4, 4, 10, True), (37, 96, 5, 2, 24, False),
                                                  (150, 128, 16, 3, 48, True), (9, 64, 40, 1, 33, True),
-                                                 (300, 32, 3, 1, 8, False)])
+                                                 (300, 32, 3, 1, 8, False), (700, 192, 6, 2, 136, True)])
 def test_routed_experts_against_the_plain_sum(ops, dtype, T, W, E, top, ff, shared):
     h = rnd(T, W, seed=T).to(dtype)
     router = rnd(E + (1 if shared else 0), W, seed=1, scale=0.3)
@@ -223,27 +223,7 @@ def test_routed_experts_against_the_plain_sum(ops, dtype, T, W, E, top, ff, shar
     close(wts, val, 1e-6)
     if shared:
         close(gate, z[:, E], 1e-6)
-    work = ops.moe_sort(idx, E)
-    n = T * top
-    offsets = work[: E + 1].cpu()
-    perm, pos_of = work[E + 1 : E + 1 + n].cpu().long(), work[E + 1 + n : E + 1 + 2 * n].cpu().long()
-    assert offsets[0] == 0 and offsets[-1] == n
-    assert torch.equal(torch.bincount(idx.cpu().flatten().long(), minlength=E), offsets[1:] - offsets[:-1])
-    assert torch.equal(pos_of[perm], torch.arange(n)) and sorted(perm.tolist()) == list(range(n))
-    sorted_experts = idx.cpu().flatten()[perm]
-    assert bool((sorted_experts[1:] >= sorted_experts[:-1]).all())
-    g = ops.expert_linear(h.cuda(), gu.cuda(), work, n, top=top, wts=wts)
-    a = ops.silu_mul(g, out_dtype=dtype, activation="silu")
-    y = ops.expert_linear(a, down.cuda(), work, n)
-    for kind in (0, 1, 2):  # the kernels give the same products
-        close(ops.expert_linear(h.cuda(), gu.cuda(), work, n, top=top, wts=wts, kind=kind), g.double().cpu(),
-              1e-5 if dtype == torch.float32 else 2e-3, f"gate|up, kernel {kind}")
-        close(ops.expert_linear(a, down.cuda(), work, n, kind=kind), y.double().cpu(),
-              1e-5 if dtype == torch.float32 else 2e-3, f"down, kernel {kind}")
-    x = rnd(T, W, seed=5)
-    into = x.clone().cuda()
-    assert ops.moe_combine(y, work, E, top, None if not shared else shared_out.cuda(), gate, into) is None
-    ref = x.to(F).clone()
+    ref = torch.zeros(T, W, dtype=F)
     for t in range(T):
         for k in range(top):
             e = int(ref_idx[t, k])
@@ -252,9 +232,28 @@ def test_routed_experts_against_the_plain_sum(ops, dtype, T, W, E, top, ff, shar
             ref[t] += down[e].to(F) @ (pp.silu(gg[:ff]) * gg[ff:])
         if shared:
             ref[t] += z[t, E] * shared_out[t].to(F)
-    close(into, ref, 2e-5 if dtype == torch.float32 else 1.5e-2)
-    alone = ops.moe_combine(y, work, E, top, None if not shared else shared_out.cuda(), gate, None)
-    close(alone, ref - x.to(F), 2e-5 if dtype == torch.float32 else 1.5e-2)
+    n = T * top
+    kinds = [None, 0] if dtype == torch.float32 else [None, 0, 1, 2] + ([3] if W % 8 == 0 and ff % 8 == 0 else [])
+    for kind in kinds:  # every kernel of the experts' products gives the same sum
+        plan = ops.moe_sort(idx, E, dtype, width=8 if W % 8 == 0 and ff % 8 == 0 else 1, kind=kind)
+        work = plan.work
+        offsets = work[: E + 1].cpu()
+        perm, pos_of = work[E + 1 : E + 1 + n].cpu().long(), work[E + 1 + n : E + 1 + 2 * n].cpu().long()
+        assert offsets[0] == 0 and offsets[-1] == n
+        assert torch.equal(torch.bincount(idx.cpu().flatten().long(), minlength=E), offsets[1:] - offsets[:-1])
+        assert torch.equal(pos_of[perm], torch.arange(n)) and sorted(perm.tolist()) == list(range(n))
+        sorted_experts = idx.cpu().flatten()[perm]
+        assert bool((sorted_experts[1:] >= sorted_experts[:-1]).all())
+        g = ops.expert_linear(h.cuda(), gu.cuda(), plan, top=top, wts=wts)
+        a = ops.silu_mul(g, out_dtype=dtype, activation="silu")
+        y = ops.expert_linear(a, down.cuda(), plan)
+        x = rnd(T, W, seed=5)
+        into = x.clone().cuda()
+        assert ops.moe_combine(y, plan, top, None if not shared else shared_out.cuda(), gate, into) is None
+        close(into, ref + x.to(F), 2e-5 if dtype == torch.float32 else 1.5e-2, f"kernel {kind}")
+        alone = ops.moe_combine(y, plan, top, None if not shared else shared_out.cuda(), gate, None)
+        close(alone, ref, 2e-5 if dtype == torch.float32 else 1.5e-2, f"kernel {kind}")
+    ops.check_kernel_errors()
 
 
 def test_router_ties_go_to_the_lower_index(ops):
