@@ -345,10 +345,11 @@ __global__ void __launch_bounds__(MM_THREADS) rows_gemm_mma_kernel(const RowsGem
 }
 
 // rows_gemv: few rows per tile (single tokens). A warp streams four weight rows at a time in
-// 16-byte pieces, two steps of k in flight, and multiplies them with up to RN rows of the tile
-// (RN = 2, 4 or 8 by the tile's row count; more rows take further passes); the rows come from L1.
-// The lanes' partial sums are added in a fixed order, so a row's result does not depend on the batch.
-constexpr int GV_WARPS = 8, GV_ROWS = 8, GV_CPW = 4, GV_COLS = GV_WARPS * GV_CPW;  // columns per block
+// 16-byte pieces, two steps of k in flight (eight loads per lane), and multiplies them with up to
+// RN rows of the tile (RN = 1, 2 or 4 by the tile's row count; more rows take further passes over
+// the weights, which then come from L2); the rows come from L1. The lanes' partial sums are added
+// in a fixed order, so a row's result does not depend on the batch.
+constexpr int GV_WARPS = 8, GV_ROWS = 4, GV_CPW = 4, GV_COLS = GV_WARPS * GV_CPW;  // columns per block
 
 template <typename TO, int RN>
 __device__ __forceinline__ void gemv_rows(const RowsGemm& g, const bf16* a, const bf16* w, TO* out,
@@ -366,18 +367,27 @@ __device__ __forceinline__ void gemv_rows(const RowsGemm& g, const bf16* a, cons
   for (int c = 0; c < GV_CPW; ++c)
 #pragma unroll
     for (int r = 0; r < RN; ++r) acc[c][r] = 0.f;
-  for (int k = lane * 8; k < K; k += 32 * 8) {
-    Vec16<bf16> wv[GV_CPW];
+  for (int k = lane * 8; k < K; k += 2 * 32 * 8) {
+    const int k2 = k + 32 * 8;
+    const bool more = k2 < K;
+    Vec16<bf16> wv[2][GV_CPW];
 #pragma unroll
-    for (int c = 0; c < GV_CPW; ++c) wv[c] = load16(wr[c] + k);
+    for (int c = 0; c < GV_CPW; ++c) {
+      wv[0][c] = load16(wr[c] + k);
+      wv[1][c] = load16(wr[c] + (more ? k2 : k));
+    }
 #pragma unroll
     for (int r = 0; r < RN; ++r) {
-      const Vec16<bf16> av = load16(ar[r] + k);
+      const Vec16<bf16> a0 = load16(ar[r] + k), a1 = load16(ar[r] + (more ? k2 : k));
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        const float x = __bfloat162float(av.v[e]);
+        const float x0 = __bfloat162float(a0.v[e]);
+        const float x1 = more ? __bfloat162float(a1.v[e]) : 0.f;
 #pragma unroll
-        for (int c = 0; c < GV_CPW; ++c) acc[c][r] = fmaf(x, __bfloat162float(wv[c].v[e]), acc[c][r]);
+        for (int c = 0; c < GV_CPW; ++c) {
+          acc[c][r] = fmaf(x0, __bfloat162float(wv[0][c].v[e]), acc[c][r]);
+          acc[c][r] = fmaf(x1, __bfloat162float(wv[1][c].v[e]), acc[c][r]);
+        }
       }
     }
   }
@@ -392,7 +402,7 @@ __device__ __forceinline__ void gemv_rows(const RowsGemm& g, const bf16* a, cons
 }
 
 template <typename TO>
-__global__ void __launch_bounds__(GV_WARPS * 32) rows_gemv_kernel(const RowsGemm g) {
+__global__ void __launch_bounds__(GV_WARPS * 32, 2) rows_gemv_kernel(const RowsGemm g) {
   pdl_trigger();
   pdl_wait();  // everything below reads what kernels before this one wrote
   __shared__ int srow[BM];
@@ -423,8 +433,8 @@ __global__ void __launch_bounds__(GV_WARPS * 32) rows_gemv_kernel(const RowsGemm
   if (n >= g.N) return;
   for (int r0 = 0; r0 < rows; r0 += GV_ROWS) {
     const int left = rows - r0;
-    if (left <= 2) gemv_rows<TO, 2>(g, a, w, out, srow, sscale, m0, r0, rows, n, lane);
-    else if (left <= 4) gemv_rows<TO, 4>(g, a, w, out, srow, sscale, m0, r0, rows, n, lane);
+    if (left == 1) gemv_rows<TO, 1>(g, a, w, out, srow, sscale, m0, r0, rows, n, lane);
+    else if (left == 2) gemv_rows<TO, 2>(g, a, w, out, srow, sscale, m0, r0, rows, n, lane);
     else gemv_rows<TO, GV_ROWS>(g, a, w, out, srow, sscale, m0, r0, rows, n, lane);
   }
 }

@@ -503,13 +503,14 @@ class CudaOps:
         """The choices sorted by expert, as row ranges and tiles for :meth:`expert_linear`: a plan
         that :meth:`moe_combine` reads too. ``dtype`` and ``width`` (of the experts' input) choose
         the kernel of the products: 0 the CUDA cores (float32), 2 the weight-streaming kernel (up
-        to 128 choices: few rows per expert), 1 mma.sync tiles, 3 tcgen05 tiles (many rows of
-        whole 16-byte vectors); ``kind`` forces one."""
+        to 48 choices: a few rows per expert; measured at 8 experts of 4096 x 2048, 2 per token:
+        16 tokens 45 us against 55 us for the tiles, 32 tokens 72 against 58), 1 mma.sync tiles,
+        3 tcgen05 tiles (more than 1024 choices, rows of whole 16-byte vectors); ``kind`` forces one."""
         n = idx.numel()
         if kind is None:
             if dtype != torch.bfloat16:
                 kind = 0
-            elif n <= 128:
+            elif n <= 48:
                 kind = 2
             else:
                 kind = 3 if (n > 1024 and width % 8 == 0) else 1
