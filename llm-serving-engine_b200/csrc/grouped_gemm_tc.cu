@@ -27,7 +27,7 @@ constexpr int BM = 256;  // output features per block: two MMAs of M = 128
 constexpr int BT = 128;  // rows per tile (MMA N)
 constexpr int BK = 64;   // k elements per stage: 128 bytes, one swizzle row
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 4;
+constexpr int STAGES = 2;
 
 using namespace tma;
 
