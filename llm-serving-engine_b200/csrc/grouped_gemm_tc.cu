@@ -13,7 +13,10 @@
 // tensor cores could consume. One thread runs the TMA pipeline, one issues the MMAs with two
 // accumulators [128 x 128] in tensor memory, four warps read them back and write out[r, n] with
 // n across lanes. Rows of the tile that lie past the expert's range (they are the next expert's,
-// or past the end) are computed and not stored; so are features past the expert's N.
+// or past the end) are computed and not stored; so are features past the expert's N. Two blocks
+// share an SM (two stages and 256 columns of tensor memory each): one block's set-up and
+// epilogue run under the other's MMAs (measured: 862 TFLOP/s against 643 with one block of four
+// stages, on 4096 rows over 8 experts of 4096 x 2048).
 //
 // Every wait on an mbarrier is bounded: on expiry the block records an error code in *error_flag
 // and leaves through the normal teardown (tensor memory is released).
