@@ -18,7 +18,7 @@ from ..config.pazivik import PazivikConfig
 from ..parts.blocks import PreNormBlockSpec
 from ..parts.embed_terms import HashedPairSpec
 from ..parts.feed_forward import SwiGLUSpec
-from ..parts.latent_attention import LatentAttentionSpec
+from ..parts.latent_attention import LatentAttentionSpec, needs_materialized_heads
 from ..parts.moe import RoutedExpertsSpec
 from ..parts.norms import RMSNormSpec
 from ..parts.positions import SinusoidSpec
@@ -42,12 +42,15 @@ def pazivik_plan(cfg: PazivikConfig) -> ModelPlan:
         win = l.mixer.window
         keep[owner[i]] = 0 if (win == 0 or keep.get(owner[i], win) == 0) else max(keep.get(owner[i], 0), win)
     layers = []
+    # a rank beyond the attention kernels' head sizes: such a layer keeps keys and values of its
+    # own (every layer its own cache layer and window) and is handed the step's latent rows
+    wide = [needs_materialized_heads(l.mixer.kv_rank) for l in cfg.layers]
     for i, l in enumerate(cfg.layers):
         m = l.mixer
         mixer = LatentAttentionSpec(
             hidden_size=w, num_heads=m.heads, head_dim=m.dim, value_dim=m.vdim, latent_rank=m.kv_rank,
-            scale=m.scale, eps=eps, window=m.window, cache_window=keep[owner[i]],
-            own_latent=m.kv_from is None, sinks=True)
+            scale=m.scale, eps=eps, window=m.window, cache_window=m.window if wide[i] else keep[owner[i]],
+            own_latent=m.kv_from is None, sinks=True, materialize=wide[i], latent_key=owner[i])
         if l.mlp is None:
             ff = None
         elif l.mlp.kind == "dense":
@@ -56,11 +59,11 @@ def pazivik_plan(cfg: PazivikConfig) -> ModelPlan:
             ff = RoutedExpertsSpec(w, l.mlp.experts, l.mlp.top, l.mlp.ff, l.mlp.shared_ff, activation="silu")
         layers.append(PreNormBlockSpec(norm_in=norm, mixer=mixer, norm_post=norm if ff is not None else None,
                                        feed_forward=ff))
-    owners = sorted(set(owner))
-    cache_id = {o: k for k, o in enumerate(owners)}
+    users = sorted({i if wide[i] else owner[i] for i in range(len(layers))})
+    cache_id = {o: k for k, o in enumerate(users)}
     return ModelPlan(
         vocab_size=cfg.vocab_size, hidden_size=w, layers=tuple(layers),
-        run_order=tuple(RunEntry(i, cache_id[owner[i]]) for i in range(len(layers))),
+        run_order=tuple(RunEntry(i, cache_id[i if wide[i] else owner[i]]) for i in range(len(layers))),
         final_norm=norm, tie_head=True, embed_position=SinusoidSpec(w, SINUSOID_BASE),
         embed_terms=(HashedPairSpec(w, cfg.bigram_buckets, cfg.bigram_mul_prev, cfg.bigram_mul_cur),),
         logit_softcap=cfg.logit_softcap)

@@ -20,6 +20,12 @@ padded with zeros when the weights are bound.
 A layer with ``own_latent=False`` has no ``Wd``: it is bound to the cache layer of another layer
 and reads the rows that layer wrote, with its own ``Wuk``, ``Wuv``, queries, window and sinks.
 ``cache_window`` is what the shared cache keeps (at least every reader's window).
+
+``materialize=True`` is the other arrangement, for a latent rank beyond the attention kernels'
+largest head size (:data:`MAX_KERNEL_DIM`): the layer keeps ``k_j`` and ``v_j`` themselves in
+pages of its own (H key/value heads of ``max(head_dim, value_dim)`` dims, zero-padded), made from
+the latent rows of this step's tokens. A layer without a latent of its own then takes those rows
+from the layer that made them earlier in the same step (``latent_key`` names it).
 """
 
 from __future__ import annotations
@@ -44,7 +50,17 @@ class LatentAttentionSpec:
     cache_window: int = 0  # what the cache layer keeps: 0 or >= the window of every layer that reads it
     own_latent: bool = True
     sinks: bool = True
+    materialize: bool = False  # keep keys and values per head instead of the latent row
+    latent_key: int = 0  # materialize: under which name this step's latent rows are handed on
     kind: str = "latent_attention"
+
+
+MAX_KERNEL_DIM = 256  # the attention kernels' largest head size
+
+
+def needs_materialized_heads(latent_rank: int) -> bool:
+    """Whether a layer of this rank has to keep keys and values instead of latent rows."""
+    return latent_rank + (-latent_rank) % 16 > MAX_KERNEL_DIM
 
 
 @MIXERS.register("latent_attention")
@@ -56,6 +72,12 @@ class LatentAttention(Mixer):
         if spec.cache_window and (spec.window == 0 or spec.window > spec.cache_window):
             raise ValueError("latent_attention: the cache keeps fewer tokens than the window reads")
         self.q_size = spec.num_heads * spec.head_dim
+        if spec.materialize:
+            widest = max(spec.head_dim, spec.value_dim)
+            self.kernel_dim = widest + (-widest) % 16
+            self.pad = 0
+            env.ops.check_attention_shape(self.kernel_dim, env.dtype, spec.num_heads, spec.num_heads)
+            return
         self.pad = (-spec.latent_rank) % 16
         self.kernel_dim = spec.latent_rank + self.pad
         env.ops.check_attention_shape(self.kernel_dim, env.dtype, spec.num_heads, 1)
@@ -82,6 +104,9 @@ class LatentAttention(Mixer):
         self.o_weight = params["o.weight"]
         self.latent_norm_weight = params.get("latent_norm.weight")
         self.sink = params.get("sink")
+        if s.materialize:
+            self._bind_materialized(params)
+            return
         # the query side's products, per head as [out, in]: Wuk^T [H, R(+pad), head_dim] and
         # Wuv [H, value_dim, R(+pad)]
         uk_t = params["uk.weight"].view(H, s.head_dim, R).transpose(1, 2)
@@ -92,7 +117,28 @@ class LatentAttention(Mixer):
         self.uk_t = uk_t.contiguous()
         self.uv = uv.contiguous()
 
+    def _bind_materialized(self, params):
+        """Every head's q, k and v rows padded with zero rows to the kernels' head size, and the
+        output projection with zero columns to match."""
+        s = self.spec
+        H, D, V, Dk, R = s.num_heads, s.head_dim, s.value_dim, self.kernel_dim, s.latent_rank
+
+        def pad_heads(w, d):  # [H * d, n] -> [H * Dk, n]
+            out = w.new_zeros(H, Dk, w.shape[1])
+            out[:, :d] = w.view(H, d, w.shape[1])
+            return out.view(H * Dk, w.shape[1])
+
+        w_in = params["in.weight"]
+        q = pad_heads(w_in[: self.q_size], D)
+        self.in_weight = torch.cat([q, w_in[self.q_size :]], 0).contiguous()
+        self.kv_weight = torch.cat([pad_heads(params["uk.weight"], D), pad_heads(params["uv.weight"], V)], 0).contiguous()
+        o = params["o.weight"].new_zeros(s.hidden_size, H, Dk)
+        o[:, :, :V] = params["o.weight"].view(s.hidden_size, H, V)
+        self.o_weight = o.view(s.hidden_size, H * Dk).contiguous()
+
     def cache_need(self):
+        if self.spec.materialize:
+            return PagedKVNeed(self.spec.num_heads, self.kernel_dim, self.spec.cache_window)
         return PagedKVNeed(1, self.kernel_dim, self.spec.cache_window, values=False)
 
     def reserve(self, max_seqs: int) -> None:
@@ -112,6 +158,8 @@ class LatentAttention(Mixer):
     def forward(self, h, step, cache, residual=None, may_defer=False):
         s, ops = self.spec, self.ops
         tables = step.block_tables[cache.group]
+        if s.materialize:
+            return self._forward_materialized(h, step, cache, tables, residual, may_defer)
         # q | latent: unrounded where the kernel set's few-rows product hands on its float32 sums,
         # in the compute dtype (the library's product rounds once) for many rows
         few = h.shape[0] <= getattr(ops, "skinny_max_rows", 0)
@@ -127,4 +175,27 @@ class LatentAttention(Mixer):
             window=s.window, k_pages=cache.k, v_pages=cache.v, block_tables=tables,
             page_tokens=cache.page_tokens, step=step, plan=step.plans[self.plan_key()], sinks=self.sink)
         o = ops.head_linear(o, 0, self.uv, out_dtype=self.env.dtype)  # [T, H * value_dim]
+        return project_into(ops, o, self.o_weight, None, self.env.residual_dtype, residual, may_defer)
+
+    def _forward_materialized(self, h, step, cache, tables, residual, may_defer):
+        """Keys and values of this step's tokens are made from their latent rows and kept in this
+        layer's own pages; the attention is the ordinary one over H key/value heads."""
+        s, ops = self.spec, self.ops
+        H, Dk = s.num_heads, self.kernel_dim
+        proj = ops.linear(h, self.in_weight, None, out_dtype=torch.float32)  # q (padded per head) | latent
+        handed = step.__dict__.setdefault("latent_rows", {})
+        if s.own_latent:
+            d = proj[:, H * Dk :].contiguous()
+            handed[s.latent_key] = ops.add_rmsnorm(d, None, self.latent_norm_weight, s.eps, out_dtype=self.env.dtype)
+        c = handed[s.latent_key]
+        kv = ops.linear(c, self.kv_weight, None, out_dtype=torch.float32)
+        qkv = torch.cat([proj[:, : H * Dk], kv], dim=1)
+        q = ops.norm_rope_kv_write(
+            qkv, num_heads=H, num_kv_heads=H, head_dim=Dk, values_are_keys=False, q_weight=None, k_weight=None,
+            eps=0.0, positions=step.positions, token_seq=step.token_seq, cos=None, sin=None, k_pages=cache.k,
+            v_pages=cache.v, block_tables=tables, page_tokens=cache.page_tokens, out_dtype=self.env.dtype)
+        o = ops.paged_attention(
+            q, num_heads=H, num_kv_heads=H, head_dim=Dk, scale=s.scale, window=s.window, k_pages=cache.k,
+            v_pages=cache.v, block_tables=tables, page_tokens=cache.page_tokens, step=step,
+            plan=step.plans[self.plan_key()], sinks=self.sink)
         return project_into(ops, o, self.o_weight, None, self.env.residual_dtype, residual, may_defer)

@@ -204,6 +204,14 @@ PAZIVIK_TINY = {
         "layers": [_lat(8, 64, 32, 128, 0.125, 32, _moe(16, 3, 48, 64)),
                    _lat(4, 32, 64, 64, 0.18, 100, _dense(192)),
                    _lat(6, 16, 16, 64, 0.25, 64, _moe(2, 1, 64, 8), kv_from=1)]}),
+    # a latent rank beyond the attention kernels' head sizes: keys and values are kept per head,
+    # and the layer that reads another's latent rows is handed them within the step
+    "P4": dict(seed=23, page_tokens=16, sharp=6, config={
+        "architecture": "Pazivik", "vocab": 150, "width": 80, "norm": {"eps": 1e-5}, "logit_softcap": 15.0,
+        "embedding": {"bigram": {"buckets": 53, "mul_cur": 11, "mul_prev": 7}},
+        "layers": [_lat(2, 16, 24, 272, 0.25, 12, _dense(96)),
+                   _lat(3, 8, 8, 272, 0.35, 30, _moe(3, 1, 16, 0), kv_from=0),
+                   _lat(2, 24, 16, 48, 0.2, 9, None)]}),
 }
 
 

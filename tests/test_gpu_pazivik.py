@@ -284,7 +284,8 @@ def gpu_runner(folder, name, num_pages, dtype, max_num_seqs=4, max_len=512):
                        max_model_len=max_len, max_num_seqs=max_num_seqs, max_num_batched_tokens=max_len)
 
 
-LENGTHS = {"P1": [5, 70, 1, 33, 49, 126, 2], "P2": [2, 40, 9, 64, 17, 100], "P3": [3, 150, 18, 77, 230]}
+LENGTHS = {"P1": [5, 70, 1, 33, 49, 126, 2], "P2": [2, 40, 9, 64, 17, 100], "P3": [3, 150, 18, 77, 230],
+           "P4": [4, 60, 1, 45, 90]}
 TOL = {"float32": (2e-4, 5e-5), "bfloat16": (0.0, 0.03)}  # (absolute, relative to the largest logit)
 
 
@@ -298,7 +299,7 @@ def expected(pazivik_dirs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["P1", "P2", "P3"])
+@pytest.mark.parametrize("name", ["P1", "P2", "P3", "P4"])
 @pytest.mark.parametrize("mode", ["whole", "decode_tail", "portions", "mixed"])
 def test_every_way_of_cutting_matches_plain(pazivik_dirs, expected, name, mode, dtype):
     reqs, exp = expected[name]

@@ -61,6 +61,11 @@ def test_plan_shares_cache_layers_and_keeps_the_widest_window():
     assert [l.mixer.cache_window for l in plan.layers] == [33, 33, 7, 7]
     assert [l.mixer.window for l in plan.layers] == [20, 33, 7, 7]
     assert plan.layers[2].feed_forward is None and not plan.layers[1].mixer.own_latent
+    # a rank beyond the kernels' head sizes: every layer of that rank keeps keys and values of its own
+    plan4 = pazivik_plan(PazivikConfig.from_dict(PAZIVIK_TINY["P4"]["config"]))
+    assert [(e.layer, e.cache) for e in plan4.run_order] == [(0, 0), (1, 1), (2, 2)]
+    assert [l.mixer.materialize for l in plan4.layers] == [True, True, False]
+    assert [l.mixer.cache_window for l in plan4.layers] == [12, 30, 9] and plan4.layers[1].mixer.latent_key == 0
     plan2 = pazivik_plan(PazivikConfig.from_dict(PAZIVIK_TINY["P2"]["config"]))
     assert [l.mixer.cache_window for l in plan2.layers] == [9, 0, 9]  # the reader sees further than the writer
 
@@ -94,10 +99,10 @@ def test_cache_layers_one_row_per_token_and_the_previous_token(pazivik_dirs):
     assert prev.k is None and prev.state.dtype == torch.int32 and tuple(prev.state.shape[1:]) == (1,)
 
 
-LENGTHS = {"P1": [5, 70, 1, 33, 49, 26], "P2": [2, 40, 9, 64, 17], "P3": [3, 150, 18, 77]}
+LENGTHS = {"P1": [5, 70, 1, 33, 49, 26], "P2": [2, 40, 9, 64, 17], "P3": [3, 150, 18, 77], "P4": [4, 60, 1, 45]}
 
 
-@pytest.mark.parametrize("name", ["P1", "P2", "P3"])
+@pytest.mark.parametrize("name", ["P1", "P2", "P3", "P4"])
 @pytest.mark.parametrize("mode", ["whole", "decode_tail", "portions", "mixed"])
 def test_every_way_of_cutting_matches_plain(pazivik_dirs, name, mode):
     folder = pazivik_dirs[name]
