@@ -430,7 +430,7 @@ void hashed_pair_add(Tensor& x, const Tensor& table, Tensor& state, const Tensor
   TORCH_CHECK(buckets > 0 && mul_prev >= 0 && mul_cur >= 0, "hashed_pair_add: bad constants");
   done(lse_hashed_pair_add(x.data_ptr<float>(), table.data_ptr(), out_code(table, "table"),
                            state.data_ptr<int>(), ids.data_ptr<int>(), positions.data_ptr<int>(),
-                           token_seq.data_ptr<int>(), cu_q.data_ptr<int>(), slots.data_ptr<int>(), T, W,
+                           token_seq.data_ptr<int>(), cu_q.data_ptr<int>(), slots.data_ptr<int>(), T, (int)slots.numel(), W,
                            (long long)buckets, (long long)mul_prev, (long long)mul_cur, stream()),
        "hashed_pair_add");
 }

@@ -174,8 +174,8 @@ int lse_decay_linear_attention(const float* proj, long long stride, float* out, 
 // token of the step.   x float32 [T, W], table [buckets + 1, W]
 int lse_hashed_pair_add(float* x, const void* table, int table_dtype, int* state, const int* ids,
                         const int* positions, const int* token_seq, const int* cu_q,
-                        const int* slots, int T, int W, long long buckets, long long mul_prev,
-                        long long mul_cur, cudaStream_t stream);
+                        const int* slots, int T, int num_seqs, int W, long long buckets,
+                        long long mul_prev, long long mul_cur, cudaStream_t stream);
 
 // x[t, i] += sin(p * freq[i / 2]) for even i, cos(...) for odd i; p = float(positions[t])
 int lse_sinusoid_add(float* x, const int* positions, const float* freq, int T, int W,

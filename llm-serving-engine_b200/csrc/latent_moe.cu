@@ -16,6 +16,8 @@
 namespace lse {
 
 // ------------------------------------------------------------------------------------ embeddings
+constexpr int EMB_SLICE = 256;  // columns per block of the sinusoid: two per thread
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 hashed_pair_add_kernel(float* __restrict__ x, const T* __restrict__ table, int* __restrict__ state,
@@ -39,7 +41,8 @@ hashed_pair_add_kernel(float* __restrict__ x, const T* __restrict__ table, int* 
   if (t == first && threadIdx.x == 0) state[slots[seq]] = ids[cu_q[seq + 1] - 1];
   const T* src = table + (size_t)row * W;
   float* dst = x + (size_t)t * W;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) dst[i] += Num<T>::to_float(src[i]);
+#pragma unroll 4
+  for (int i = threadIdx.x; i < W; i += 128) dst[i] += Num<T>::to_float(src[i]);
 }
 
 __global__ void __launch_bounds__(128)
@@ -50,9 +53,14 @@ sinusoid_add_kernel(float* __restrict__ x, const int* __restrict__ positions,
   const int t = blockIdx.x;
   const float p = (float)positions[t];
   float* dst = x + (size_t)t * W;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const float ang = p * freq[i >> 1];  // the angle is a float32 product, as positions are float32
-    dst[i] += (i & 1) ? cosf(ang) : sinf(ang);
+  const int i0 = blockIdx.y * EMB_SLICE + threadIdx.x;
+#pragma unroll
+  for (int j = 0; j < EMB_SLICE / 128; ++j) {
+    const int i = i0 + j * 128;
+    if (i < W) {
+      const float ang = p * freq[i >> 1];  // the angle is a float32 product, as positions are float32
+      dst[i] += (i & 1) ? cosf(ang) : sinf(ang);
+    }
   }
 }
 
@@ -440,8 +448,9 @@ __global__ void __launch_bounds__(GV_WARPS * 32, 2) rows_gemv_kernel(const RowsG
 }
 
 // ------------------------------------------------------------------------------------ routing
-// One block of eight warps per token: warp w takes the router's rows w, w + 8, ... (scores =
-// sigmoid(router . h) in float32, a row's sum in an order that depends on nothing but the width);
+// One block of eight warps per token. Every router row is shared by the eight warps (warp w takes
+// the columns w * 32 + lane, + 256, ...); the warps' partial sums are added in the order of the
+// warps, so a score depends on nothing but the width. scores = sigmoid(router . h) in float32;
 // then the first warp picks the `top` largest (the lower index on a tie) with their scores. Row E
 // of the router, if there is one, is the shared expert's gate.
 constexpr int ROUTE_WARPS = 8;
@@ -453,20 +462,27 @@ moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ router, int
                  float* __restrict__ gate) {
   pdl_trigger();
   pdl_wait();  // everything below reads what kernels before this one wrote
-  extern __shared__ float s[];  // [E]
+  extern __shared__ float s[];  // [E + 1] scores, then [E + 1][ROUTE_WARPS] partial sums
+  float* part = s + E + 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const size_t t = blockIdx.x;
   const TH* row = h + t * W;
-  for (int e = warp; e < E + has_gate; e += ROUTE_WARPS) {
+  const int rows = E + has_gate;
+  for (int e = 0; e < rows; ++e) {
     const float* r = router + (size_t)e * W;
     float d = 0.f;
-    for (int i = lane; i < W; i += 32) d = fmaf(Num<TH>::to_float(row[i]), r[i], d);
+    for (int i = threadIdx.x; i < W; i += ROUTE_WARPS * 32) d = fmaf(Num<TH>::to_float(row[i]), r[i], d);
     d = warp_sum(d);
+    if (lane == 0) part[e * ROUTE_WARPS + warp] = d;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < rows; e += ROUTE_WARPS * 32) {
+    float d = 0.f;
+#pragma unroll
+    for (int w = 0; w < ROUTE_WARPS; ++w) d += part[e * ROUTE_WARPS + w];
     const float sg = 1.f / (1.f + expf(-d));
-    if (lane == 0) {
-      if (e < E) s[e] = sg;
-      else gate[t] = sg;
-    }
+    if (e < E) s[e] = sg;
+    else gate[t] = sg;
   }
   __syncthreads();
   if (warp != 0) return;
@@ -558,7 +574,10 @@ moe_gather_rows_kernel(const bf16* __restrict__ a, const int* __restrict__ perm,
   store16(out + (size_t)r * K + c * 8, load16(a + (size_t)(perm[r] / top) * K + c * 8));
 }
 
-// x[t] (or out[t]) (+)= sum_k y[pos_of[t * top + k]] + gate[t] * shared[t]
+// x[t] (or out[t]) (+)= sum_k y[pos_of[t * top + k]] + gate[t] * shared[t]; a block per token and
+// slice of 512 columns, four columns per thread (the experts' rows are added in the order k = 0, 1, ...)
+constexpr int COMBINE_SLICE = 512;
+
 __global__ void __launch_bounds__(128)
 moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of, int top,
                    const float* __restrict__ shared_out, const float* __restrict__ gate,
@@ -567,12 +586,26 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of, 
   pdl_wait();  // everything below reads what kernels before this one wrote
   const int t = blockIdx.x;
   const float g = gate ? gate[t] : 0.f;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    float v = 0.f;
-    for (int k = 0; k < top; ++k) v += y[(size_t)pos_of[(size_t)t * top + k] * W + i];
-    if (shared_out) v += g * shared_out[(size_t)t * W + i];
+  const int i0 = blockIdx.y * COMBINE_SLICE + threadIdx.x;
+  float v[COMBINE_SLICE / 128];
+#pragma unroll
+  for (int j = 0; j < COMBINE_SLICE / 128; ++j) v[j] = 0.f;
+  for (int k = 0; k < top; ++k) {
+    const float* row = y + (size_t)pos_of[(size_t)t * top + k] * W;
+#pragma unroll
+    for (int j = 0; j < COMBINE_SLICE / 128; ++j) {
+      const int i = i0 + j * 128;
+      if (i < W) v[j] += row[i];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < COMBINE_SLICE / 128; ++j) {
+    const int i = i0 + j * 128;
+    if (i >= W) continue;
+    float r = v[j];
+    if (shared_out) r += g * shared_out[(size_t)t * W + i];
     float* o = out + (size_t)t * W + i;
-    *o = accumulate ? *o + v : v;
+    *o = accumulate ? *o + r : r;
   }
 }
 
@@ -584,10 +617,11 @@ using namespace lse;
 
 extern "C" int lse_hashed_pair_add(float* x, const void* table, int table_dtype, int* state,
                                    const int* ids, const int* positions, const int* token_seq,
-                                   const int* cu_q, const int* slots, int T, int W, long long buckets,
-                                   long long mul_prev, long long mul_cur, cudaStream_t stream) {
+                                   const int* cu_q, const int* slots, int T, int num_seqs, int W,
+                                   long long buckets, long long mul_prev, long long mul_cur,
+                                   cudaStream_t stream) {
   if (T <= 0) return LSE_OK;
-  if (buckets <= 0 || W <= 0) return LSE_BAD_ARGUMENT;
+  if (buckets <= 0 || W <= 0 || num_seqs <= 0) return LSE_BAD_ARGUMENT;
   if (table_dtype == LSE_F32)
     launch(hashed_pair_add_kernel<float>, T, 128, 0, stream, x, (const float*)table, state, ids, positions, token_seq,
                                                          cu_q, slots, W, buckets, mul_prev, mul_cur);
@@ -602,7 +636,7 @@ extern "C" int lse_hashed_pair_add(float* x, const void* table, int table_dtype,
 extern "C" int lse_sinusoid_add(float* x, const int* positions, const float* freq, int T, int W,
                                 cudaStream_t stream) {
   if (T <= 0) return LSE_OK;
-  launch(sinusoid_add_kernel, T, 128, 0, stream, x, positions, freq, W);
+  launch(sinusoid_add_kernel, dim3(T, (W + EMB_SLICE - 1) / EMB_SLICE), 128, 0, stream, x, positions, freq, W);
   return LSE_CHECK_LAUNCH();
 }
 
@@ -692,8 +726,8 @@ extern "C" int lse_moe_route(const void* h, int h_dtype, const float* router, in
                              int has_gate, int top, int* idx, float* wts, float* gate,
                              cudaStream_t stream) {
   if (T <= 0) return LSE_OK;
-  if (E <= 0 || top <= 0 || top > E || E > 2048 || (has_gate && !gate)) return LSE_BAD_ARGUMENT;
-  const size_t smem = (size_t)E * sizeof(float);
+  if (E <= 0 || top <= 0 || top > E || E > 1024 || (has_gate && !gate)) return LSE_BAD_ARGUMENT;
+  const size_t smem = (size_t)(E + 1) * (1 + ROUTE_WARPS) * sizeof(float);
   if (h_dtype == LSE_F32)
     launch(moe_route_kernel<float>, T, ROUTE_WARPS * 32, smem, stream, (const float*)h, router, W, E, has_gate, top,
                                                                    idx, wts, gate);
@@ -730,6 +764,7 @@ extern "C" int lse_moe_combine(const float* y, const int* pos_of, int top, const
                                cudaStream_t stream) {
   if (T <= 0) return LSE_OK;
   if (shared_out && !gate) return LSE_BAD_ARGUMENT;
-  launch(moe_combine_kernel, T, 128, 0, stream, y, pos_of, top, shared_out, gate, out, accumulate, W);
+  launch(moe_combine_kernel, dim3(T, (W + COMBINE_SLICE - 1) / COMBINE_SLICE), 128, 0, stream, y, pos_of, top,
+         shared_out, gate, out, accumulate, W);
   return LSE_CHECK_LAUNCH();
 }

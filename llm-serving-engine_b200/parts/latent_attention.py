@@ -160,10 +160,9 @@ class LatentAttention(Mixer):
         tables = step.block_tables[cache.group]
         if s.materialize:
             return self._forward_materialized(h, step, cache, tables, residual, may_defer)
-        # q | latent: unrounded where the kernel set's few-rows product hands on its float32 sums,
-        # in the compute dtype (the library's product rounds once) for many rows
-        few = h.shape[0] <= getattr(ops, "skinny_max_rows", 0)
-        proj = ops.linear(h, self.in_weight, None, out_dtype=torch.float32 if few else self.env.dtype)
+        # q | latent in the compute dtype (one rounding of the product, whatever the number of rows:
+        # the per-head products that follow take operands of that dtype on every kernel)
+        proj = ops.linear(h, self.in_weight, None, out_dtype=self.env.dtype)
         if s.own_latent:
             if not cache.writes:
                 raise RuntimeError("a latent-attention layer with its own latent must fill its cache layer")
